@@ -34,11 +34,17 @@ from ..native import HostCore
 
 @dataclasses.dataclass(frozen=True)
 class GroupSpec:
-    """A cache group: which tokens its layers read (``window`` None = all) and its pool."""
+    """A cache group: which tokens its layers read (``window`` None = all; ``chunk`` C: from the start of the
+    query's own run of C positions on) and its pool."""
     key: Tuple
     window: Optional[int]
     page_size: int
     num_pages: int
+    chunk: Optional[int] = None
+
+    @property
+    def keeps_all(self) -> bool:
+        return self.window is None and self.chunk is None
 
 
 class _Names:
@@ -154,9 +160,9 @@ class CacheManager:
         if max_requests <= 0:
             raise InvalidArgument("at least one state slot is needed")
         if max_context is None:
-            max_context = max([g.num_pages * g.page_size for g in self.groups if g.window is None] or
+            max_context = max([g.num_pages * g.page_size for g in self.groups if g.keeps_all] or
                               [g.num_pages * g.page_size for g in self.groups] or [1])
-        self.core = HostCore([(g.window, g.page_size, g.num_pages) for g in self.groups], max_requests,
+        self.core = HostCore([(g.window, g.page_size, g.num_pages, g.chunk) for g in self.groups], max_requests,
                              max_tokens_per_step or max(max_requests, 1), max(1, max_context))
         self._names = _Names()
         self.pools = [PagePool(g.num_pages, self.core, i, self._names) for i, g in enumerate(self.groups)]
@@ -189,10 +195,12 @@ class CacheManager:
     def first_needed_page(self, g: int, ctx_len: int) -> int:
         """Logical index of the first page a query at position >= ctx_len can still read."""
         spec = self.groups[g]
-        if spec.window is None:
-            return 0
-        first_key = ctx_len - spec.window + 1
-        return max(0, first_key) // spec.page_size
+        first_key = 0
+        if spec.window is not None:
+            first_key = max(0, ctx_len - spec.window + 1)
+        if spec.chunk is not None:
+            first_key = max(first_key, ctx_len // spec.chunk * spec.chunk)
+        return first_key // spec.page_size
 
     def pages_needed(self, req_id: Hashable, n_new: int) -> List[int]:
         """Pages each group would have to take to hold ``n_new`` more tokens of the request."""

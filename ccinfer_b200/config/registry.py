@@ -48,8 +48,10 @@ def _builtin():
         from .tugelorn import TugelornConfig
         register_architecture("Tugelorn", TugelornConfig.from_json, tugelorn.build_plan,
                               complete_config=lambda cfg, shapes: cfg.with_shapes(shapes))
-
-
+    if "Burolorn" not in _REGISTRY:
+        from ..architectures import burolorn
+        from .burolorn import BurolornConfig
+        register_architecture("Burolorn", BurolornConfig.from_json, burolorn.build_plan)
     if "Dufizen" not in _REGISTRY:
         from ..architectures import dufizen
         from .dufizen import DufizenConfig

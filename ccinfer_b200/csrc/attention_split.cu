@@ -56,7 +56,7 @@ attention_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
                        const int* __restrict__ positions, const int* __restrict__ entry_of_token,
                        const int* __restrict__ block_table, int bt_stride, int n_entries, int row0, int nq, int nkv,
                        int hd, int page_size, int num_pages, int window, float scale, int num_splits,
-                       int* status) {
+                       AttnExtra ex, int* status) {
   ccb::pdl_begin();
   extern __shared__ float smem[];  // [warps][GT][hd] accumulators, then [warps][GT] max, [warps][GT] sum
   const int G = nq / nkv;
@@ -100,7 +100,7 @@ attention_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
         }
       }
     const int* bt = block_table + (size_t)b * bt_stride;
-    const int j0 = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int j0 = first_visible_key(p, window, ex.chunk);
     const int first_tile = j0 >> kTileShift, last_tile = p >> kTileShift;
     const int n_tiles = last_tile - first_tile + 1;
     const int per_split = (n_tiles + num_splits - 1) / num_splits;
@@ -257,7 +257,15 @@ attention_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
     }
     const int h = h0 + g;
     if (num_splits == 1) {
-      out[((size_t)t * nq + h) * hd + d] = from_f32<T>(ll > 0.f ? a / ll : 0.f);
+      if (ex.sink != nullptr && !padded) {   // the sink's term: one more in the denominator, nothing in the sum
+        const float sk = ex.sink[h];
+        const float m2 = fmaxf(mm, sk);
+        const float f = mm == -CUDART_INF_F ? 0.f : exp_of<T>(mm - m2);
+        a *= f;
+        ll = ll * f + exp_of<T>(sk - m2);
+      }
+      const float gt = padded ? 1.f : attn_gate<T>(ex, t, h);
+      out[((size_t)t * nq + h) * hd + d] = from_f32<T>(ll > 0.f ? a / ll * gt : 0.f);
     } else {
       const size_t slot = ((size_t)r * nq + h) * num_splits + split;
       part_acc[slot * hd + d] = a;
@@ -271,24 +279,29 @@ attention_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
 
 template <typename T>
 __global__ void attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
-                                       const float* __restrict__ part_ml, int row0, int nq, int hd, int num_splits) {
+                                       const float* __restrict__ part_ml, int row0, int nq, int hd, int num_splits,
+                                       AttnExtra ex) {
   ccb::pdl_begin();
   const int r = blockIdx.x, h = blockIdx.y;
   const size_t base = ((size_t)r * nq + h) * num_splits;
   float mm = -CUDART_INF_F;
   for (int s = 0; s < num_splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
   T* o = out + ((size_t)(row0 + r) * nq + h) * hd;
+  const bool seen = mm != -CUDART_INF_F;   // (a padded row has no partial result that saw a key)
+  if (seen && ex.sink != nullptr) mm = fmaxf(mm, ex.sink[h]);
   if (mm == -CUDART_INF_F) {
     for (int d = threadIdx.x; d < hd; d += blockDim.x) o[d] = from_f32<T>(0.f);
     return;
   }
   float ll = 0.f;
   for (int s = 0; s < num_splits; ++s) ll += part_ml[(base + s) * 2 + 1] * exp_of<T>(part_ml[(base + s) * 2] - mm);
+  if (ex.sink != nullptr) ll += exp_of<T>(ex.sink[h] - mm);
+  const float gt = attn_gate<T>(ex, row0 + r, h);
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float a = 0.f;
     for (int s = 0; s < num_splits; ++s)
       a += part_acc[(base + s) * hd + d] * exp_of<T>(part_ml[(base + s) * 2] - mm);
-    o[d] = from_f32<T>(a / ll);
+    o[d] = from_f32<T>(a / ll * gt);
   }
 }
 
@@ -296,77 +309,91 @@ template <typename T, int GT, int NV>
 int launch_split(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_acc, float* part_ml,
                  const int* positions, const int* entry_of_token, const int* block_table, int bt_stride,
                  int n_entries, int row0, int n_rows, int nq, int nkv, int hd, int page_size, int num_pages,
-                 int window, float scale, int num_splits, int* status, cudaStream_t stream) {
+                 int window, float scale, int num_splits, AttnExtra ex, int* status, cudaStream_t stream) {
   const int G = nq / nkv, gchunks = (G + GT - 1) / GT;
   dim3 grid(n_rows, nkv * gchunks, num_splits);
   const size_t smem = sizeof(float) * (kWarps * GT * hd + 2 * kWarps * GT);
   ccb_launch(attention_split_kernel<T, GT, NV>, grid, kWarps * 32, smem, stream, 
       (const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out, part_acc, part_ml, positions, entry_of_token,
-      block_table, bt_stride, n_entries, row0, nq, nkv, hd, page_size, num_pages, window, scale, num_splits, status);
+      block_table, bt_stride, n_entries, row0, nq, nkv, hd, page_size, num_pages, window, scale, num_splits, ex, status);
   int rc = ccb_launch_status();
   if (rc != 0 || num_splits == 1) return rc;
   if (std::is_same<T, float>::value)
     ccb_launch(attention_merge_kernel<float>, dim3(n_rows, nq), 128, 0, stream, (float*)out, part_acc, part_ml, row0, nq, hd,
-                                                                         num_splits);
+                                                                         num_splits, ex);
   else
     ccb_launch(attention_merge_kernel<__nv_bfloat16>, dim3(n_rows, nq), 128, 0, stream, (__nv_bfloat16*)out, part_acc,
-                                                                                 part_ml, row0, nq, hd, num_splits);
+                                                                                 part_ml, row0, nq, hd, num_splits, ex);
   return ccb_launch_status();
 }
 
 template <typename T, int GT>
 int pick_nv(int hd, const void* q, const void* k, const void* v, void* out, float* pa, float* pm, const int* pos,
             const int* eot, const int* bt, int bts, int ne, int row0, int n_rows, int nq, int nkv, int ps, int np,
-            int window, float scale, int splits, int* status, cudaStream_t st) {
+            int window, float scale, int splits, AttnExtra ex, int* status, cudaStream_t st) {
   if (hd <= 64)
     return launch_split<T, GT, 1>(q, k, v, out, pa, pm, pos, eot, bt, bts, ne, row0, n_rows, nq, nkv, hd, ps, np,
-                                  window, scale, splits, status, st);
+                                  window, scale, splits, ex, status, st);
   if (hd <= 128)
     return launch_split<T, GT, 2>(q, k, v, out, pa, pm, pos, eot, bt, bts, ne, row0, n_rows, nq, nkv, hd, ps, np,
-                                  window, scale, splits, status, st);
+                                  window, scale, splits, ex, status, st);
   return launch_split<T, GT, 4>(q, k, v, out, pa, pm, pos, eot, bt, bts, ne, row0, n_rows, nq, nkv, hd, ps, np,
-                                window, scale, splits, status, st);
+                                window, scale, splits, ex, status, st);
 }
 
 template <typename T>
 int pick_gt(int hd, const void* q, const void* k, const void* v, void* out, float* pa, float* pm, const int* pos,
             const int* eot, const int* bt, int bts, int ne, int row0, int n_rows, int nq, int nkv, int ps, int np,
-            int window, float scale, int splits, int* status, cudaStream_t st) {
+            int window, float scale, int splits, AttnExtra ex, int* status, cudaStream_t st) {
   const int G = nq / nkv;
   // wide heads keep fewer q heads per block so that the accumulators stay in registers
   if (G >= 4 && hd <= 128)
     return pick_nv<T, 4>(hd, q, k, v, out, pa, pm, pos, eot, bt, bts, ne, row0, n_rows, nq, nkv, ps, np, window,
-                         scale, splits, status, st);
+                         scale, splits, ex, status, st);
   if (G >= 2)
     return pick_nv<T, 2>(hd, q, k, v, out, pa, pm, pos, eot, bt, bts, ne, row0, n_rows, nq, nkv, ps, np, window,
-                         scale, splits, status, st);
+                         scale, splits, ex, status, st);
   return pick_nv<T, 1>(hd, q, k, v, out, pa, pm, pos, eot, bt, bts, ne, row0, n_rows, nq, nkv, ps, np, window,
-                       scale, splits, status, st);
+                       scale, splits, ex, status, st);
 }
 
 }  // namespace
 
 // Scratch: part_acc holds n_rows * nq * num_splits * hd floats, part_ml n_rows * nq * num_splits * 2
 // (both unused with one split).  Rows row0 .. row0 + n_rows - 1 of q / out / positions are handled.
+// chunk, sink, gate, gate_stride: see AttnExtra (0 / null: none).
+CCB_API int ccb_attention_split_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                   float* part_acc, float* part_ml, const int* positions,
+                                   const int* entry_of_token, const int* block_table, int bt_stride, int n_entries,
+                                   int row0, int n_rows, int nq, int nkv, int hd, int page_size, int num_pages,
+                                   int window, float scale, int num_splits, int chunk, const float* sink,
+                                   const void* gate, int gate_stride, int dtype, int* status, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (hd <= 0 || hd % 8 != 0 || hd > 256 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 ||
+      bt_stride <= 0 || num_splits <= 0 || num_splits > 64 || chunk < 0)
+    return CCB_REFUSE_SIZE;
+  if (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return CCB_REFUSE_ARG;
+  if (gate != nullptr && gate_stride < nq) return CCB_REFUSE_ARG;
+  const AttnExtra ex{chunk, sink, gate, gate_stride};
+  if (dtype == CCB_F32)
+    return pick_gt<float>(hd, q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
+                          bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window, scale,
+                          num_splits, ex, status, stream);
+  if (dtype == CCB_BF16)
+    return pick_gt<__nv_bfloat16>(hd, q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
+                                  block_table, bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages,
+                                  window, scale, num_splits, ex, status, stream);
+  return CCB_REFUSE_DTYPE;
+}
+
 CCB_API int ccb_attention_split(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_acc,
                                 float* part_ml, const int* positions, const int* entry_of_token,
                                 const int* block_table, int bt_stride, int n_entries, int row0, int n_rows, int nq,
                                 int nkv, int hd, int page_size, int num_pages, int window, float scale,
                                 int num_splits, int dtype, int* status, cudaStream_t stream) {
-  if (n_rows <= 0) return 0;
-  if (hd <= 0 || hd % 8 != 0 || hd > 256 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 ||
-      bt_stride <= 0 || num_splits <= 0 || num_splits > 64)
-    return CCB_REFUSE_SIZE;
-  if (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return CCB_REFUSE_ARG;
-  if (dtype == CCB_F32)
-    return pick_gt<float>(hd, q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
-                          bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window, scale,
-                          num_splits, status, stream);
-  if (dtype == CCB_BF16)
-    return pick_gt<__nv_bfloat16>(hd, q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
-                                  block_table, bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages,
-                                  window, scale, num_splits, status, stream);
-  return CCB_REFUSE_DTYPE;
+  return ccb_attention_split_ex(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
+                                bt_stride, n_entries, row0, n_rows, nq, nkv, hd, page_size, num_pages, window, scale,
+                                num_splits, 0, nullptr, nullptr, 0, dtype, status, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -33,6 +33,7 @@ GROUPS = {
         "elementwise.cu",
         "norm.cu",
         "rope_kv.cu",
+        "short_conv.cu",
         "delta_rule.cu",
         "linear_attention.cu",
         "latent_attention.cu",

@@ -115,6 +115,36 @@ __device__ __forceinline__ float glu_act(const CcbGluAct a, float g, float u) {
   return g / (1.f + __expf(-g)) * u;
 }
 
+// What an attention kernel takes beside keys and values (all optional):
+//   chunk  > 0: a query at position p sees only keys from floor(p / chunk) * chunk on (runs of `chunk` positions
+//          counted from the start of the sequence), on top of a window if there is one;
+//   sink   float [q heads]: one more term exp(sink[h]) in the softmax denominator of head h, with no key and no
+//          value, not scaled, counted once per query;
+//   gate   [tokens, gate_stride] in the compute type: head h's result is multiplied by sigmoid(gate[t, h]).
+struct AttnExtra {
+  int chunk;
+  const float* sink;
+  const void* gate;
+  int gate_stride;
+};
+
+// The first key position a query at position p sees (both bounds are non-decreasing in p).
+__device__ __forceinline__ int first_visible_key(int p, int window, int chunk) {
+  int j0 = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  if (chunk > 0) {
+    const int c0 = (p / chunk) * chunk;
+    j0 = c0 > j0 ? c0 : j0;
+  }
+  return j0;
+}
+
+template <typename T>
+__device__ __forceinline__ float attn_gate(const AttnExtra& ex, int t, int h) {
+  if (ex.gate == nullptr) return 1.f;
+  const float z = to_f32(static_cast<const T*>(ex.gate)[(size_t)t * ex.gate_stride + h]);
+  return 1.f / (1.f + expf(-z));
+}
+
 __device__ __forceinline__ void set_status(int* status, int bit) {
   if (status != nullptr) atomicOr(status, bit);
 }

@@ -46,6 +46,8 @@ typedef struct ccinfer_group {
   int window;     /* <= 0: every earlier token; W > 0: the last W tokens (pages behind the window are given back) */
   int page_size;  /* tokens per page */
   int num_pages;  /* pages of the pool */
+  int chunk;      /* C > 0: a query at position p reads the tokens from floor(p / C) * C on (pages behind the run of
+                     the next token are given back); may stand beside a window */
 } ccinfer_group;
 
 typedef struct ccinfer_options {

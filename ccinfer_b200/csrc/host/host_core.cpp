@@ -214,8 +214,10 @@ struct ccinfer_engine {
 
   // logical index of the first page a query at position >= ctx_len can still read
   int first_needed_page(int g, int ctx_len) const {
-    if (groups[g].window <= 0) return 0;
-    return std::max(0, ctx_len - groups[g].window + 1) / groups[g].page_size;
+    int first_key = 0;
+    if (groups[g].window > 0) first_key = std::max(0, ctx_len - groups[g].window + 1);
+    if (groups[g].chunk > 0) first_key = std::max(first_key, ctx_len / groups[g].chunk * groups[g].chunk);
+    return first_key / groups[g].page_size;
   }
 
   void undo(Sequence& s) {
@@ -257,7 +259,7 @@ struct ccinfer_engine {
     s.taken.assign(groups.size(), 0);
     std::vector<int> stale;
     for (size_t g = 0; g < groups.size(); ++g) {
-      if (groups[g].window <= 0) continue;
+      if (groups[g].window <= 0 && groups[g].chunk <= 0) continue;
       auto& t = s.tables[g];
       const int first = std::min(first_needed_page((int)g, s.ctx_len), (int)t.size());
       stale.clear();

@@ -158,7 +158,7 @@ struct ccinfer_scheduler {
     // request moves on: its pool bounds the size of a portion, not the length of a prompt)
     long long pool_tokens = -1;
     for (const auto& g : groups)
-      if (g.window <= 0) {
+      if (g.window <= 0 && g.chunk <= 0) {
         const long long t = (long long)g.num_pages * g.page_size;
         pool_tokens = pool_tokens < 0 ? t : std::min(pool_tokens, t);
       }

@@ -1,9 +1,11 @@
 // Mixture of experts: the router's choice, and the activation of the experts' first products.
 //
-// Router (float throughout): s = softmax(z) over all experts; choice scores c = s + correction; the experts
-// form `groups` equal groups of neighbours, a group's score is its largest c, only experts of the `keep` best
-// groups can be chosen (the others count as minus infinity); the `top` largest c are chosen (ties: the lower
-// index); the weight of a chosen expert is its s, not renormalised.
+// Router (float throughout): s = softmax(z) over all experts, or sigmoid(z) each (RouteRule.score_fn); choice
+// scores c = s + correction; the experts form `groups` equal groups of neighbours, a group's score is its largest
+// c, or the sum of its two largest (RouteRule.group_top), only experts of the `keep` best groups can be chosen (the
+// others count as minus infinity); the `top` largest c are chosen (ties: the lower index); the weight of a
+// chosen expert is its s, where RouteRule.renorm says so divided by the chosen ones' sum (+ 1e-20), times
+// RouteRule.scale.
 //
 //   moe_route      a warp per token: idx [T, top] (int32, in the order chosen), wts [T, top], and the same as a
 //                  dense row dense_w [T, E] (s where chosen, else 0)
@@ -19,6 +21,13 @@ namespace {
 
 constexpr int kRouteWarps = 4;
 
+struct RouteRule {
+  int score_fn;    // 0: softmax over the experts; 1: sigmoid of each logit
+  int group_top;   // a group's score: the sum of this many of its largest choice scores (1 or 2)
+  int renorm;      // 1: the chosen scores are divided by their sum (+ 1e-20)
+  float scale;     // the weights are multiplied by this last
+};
+
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -32,20 +41,26 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 __device__ __forceinline__ void route_token(const float* __restrict__ logits, int ldl,
                                             const float* __restrict__ correction, int* __restrict__ idx,
                                             float* __restrict__ wts, float* __restrict__ dense_w, int t, int E,
-                                            int groups, int keep, int top, float* s, int lane) {
+                                            int groups, int keep, int top, float* s, int lane,
+                                            const RouteRule rule) {
   float* c = s + E;
   float* gs = c + E;
   const float* z = logits + (size_t)t * ldl;
-  float mx = -CUDART_INF_F;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) {
-    const float v = expf(z[e] - mx);
-    s[e] = v;
-    sum += v;
+  float sum = 1.f;
+  if (rule.score_fn == 1) {
+    for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-z[e]));
+  } else {
+    float mx = -CUDART_INF_F;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float v = expf(z[e] - mx);
+      s[e] = v;
+      sum += v;
+    }
+    sum = warp_sum(sum);
   }
-  sum = warp_sum(sum);
   for (int e = lane; e < E; e += 32) {
     s[e] = s[e] / sum;
     c[e] = s[e] + (correction ? correction[e] : 0.f);
@@ -55,9 +70,13 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, in
   if (groups > 1 && keep < groups) {
     const int gsz = E / groups;
     for (int g = lane; g < groups; g += 32) {
-      float m = -CUDART_INF_F;
-      for (int j = 0; j < gsz; ++j) m = fmaxf(m, c[g * gsz + j]);
-      gs[g] = m;
+      float m = -CUDART_INF_F, m2 = -CUDART_INF_F;   // the largest and the one after it
+      for (int j = 0; j < gsz; ++j) {
+        const float v = c[g * gsz + j];
+        if (v > m) m2 = m, m = v;
+        else if (v > m2) m2 = v;
+      }
+      gs[g] = (rule.group_top >= 2 && gsz >= 2) ? m + m2 : m;
     }
     __syncwarp();
     // the best `keep` groups are marked by +inf in gs, one at a time
@@ -90,20 +109,34 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, in
     }
     __syncwarp();
   }
+  if ((rule.renorm || rule.scale != 1.f) && lane == 0) {   // (lane 0 wrote the weights it reads here)
+    float f = rule.scale;
+    if (rule.renorm) {
+      float tot = 0.f;
+      for (int k = 0; k < top; ++k) tot += wts[(size_t)t * top + k];
+      f = rule.scale / (tot + 1e-20f);
+    }
+    for (int k = 0; k < top; ++k) {
+      const float w = wts[(size_t)t * top + k] * f;
+      wts[(size_t)t * top + k] = w;
+      if (dense_w) dense_w[(size_t)t * E + idx[(size_t)t * top + k]] = w;
+    }
+  }
+  __syncwarp();
 }
 
 // shared memory: a warp's scratch of route_token per warp
 __global__ void __launch_bounds__(kRouteWarps * 32)
 moe_route_kernel(const float* __restrict__ logits, int ldl, const float* __restrict__ correction,
                  int* __restrict__ idx, float* __restrict__ wts, float* __restrict__ dense_w, int rows, int E,
-                 int groups, int keep, int top) {
+                 int groups, int keep, int top, RouteRule rule) {
   ccb::pdl_begin();
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * kRouteWarps + warp;
   if (t >= rows) return;
   route_token(logits, ldl, correction, idx, wts, dense_w, t, E, groups, keep, top,
-              smem + (size_t)warp * (2 * E + groups), lane);
+              smem + (size_t)warp * (2 * E + groups), lane, rule);
 }
 
 template <typename T>
@@ -171,19 +204,48 @@ moe_dense_act_vec_kernel(T* __restrict__ act, int ld, const float* __restrict__ 
   }
 }
 
+// The gated form of the same: the product's row holds all gate columns [E F + shared] and then all up columns;
+// act[t, c] = silu(gate) * up * weight, weight = dense_w[t, c / F] for an expert's columns (exact zeros where it
+// was not chosen) and sigmoid(shared_gate[t * sg_stride]) for the shared expert's (1 where shared_gate is null).
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_dense_glu_act_kernel(T* __restrict__ act, int lda, const T* __restrict__ gu, int ldg,
+                         const float* __restrict__ dense_w, const float* __restrict__ shared_gate, int sg_stride,
+                         int rows, int E, int F, int shared) {
+  ccb::pdl_begin();
+  const int width = E * F + shared;
+  const size_t total = (size_t)rows * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / width;
+    const int c = (int)(i - t * width);
+    float w;
+    if (c < E * F) w = dense_w[t * E + c / F];
+    else w = shared_gate ? 1.f / (1.f + expf(-shared_gate[t * sg_stride])) : 1.f;
+    float v = 0.f;
+    if (w != 0.f) {
+      const float g = to_f32(gu[t * ldg + c]), u = to_f32(gu[t * ldg + width + c]);
+      v = g / (1.f + expf(-g)) * u * w;
+    }
+    act[t * lda + c] = from_f32<T>(v);
+  }
+}
+
 }  // namespace
 
 CCB_API int ccb_moe_route(const float* logits, int ldl, const float* correction, int* idx, float* wts,
-                          float* dense_w, int rows, int E, int groups, int keep, int top, cudaStream_t stream) {
+                          float* dense_w, int rows, int E, int groups, int keep, int top, int score_fn,
+                          int group_top, int renorm, float scale, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
       top > (E / groups) * keep)
     return CCB_REFUSE_SIZE;
+  if (score_fn < 0 || score_fn > 1 || group_top < 1 || group_top > 2) return CCB_REFUSE_ARG;
+  const RouteRule rule{score_fn, group_top, renorm ? 1 : 0, scale};
   const size_t smem = (size_t)kRouteWarps * (2 * E + groups) * sizeof(float);
   if (smem > 96 * 1024) return CCB_REFUSE_SIZE;
   cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   ccb_launch(moe_route_kernel, dim3((rows + kRouteWarps - 1) / kRouteWarps), dim3(kRouteWarps * 32), smem, stream,
-             logits, ldl, correction, idx, wts, dense_w, rows, E, groups, keep, top);
+             logits, ldl, correction, idx, wts, dense_w, rows, E, groups, keep, top, rule);
   return ccb_launch_status();
 }
 
@@ -313,14 +375,14 @@ moe_route_sort_kernel(const float* __restrict__ logits, int ldl, const float* __
                       int* __restrict__ idx, float* __restrict__ wts, int rows, int E, int groups, int keep, int top,
                       int BM, int max_tiles, int* __restrict__ src_row, float* __restrict__ row_w,
                       int* __restrict__ pair_pos, int* __restrict__ tile_e, int* __restrict__ tile_r0,
-                      int* __restrict__ tile_n) {
+                      int* __restrict__ tile_n, RouteRule rule) {
   ccb::pdl_begin();
   extern __shared__ int sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* scratch = reinterpret_cast<float*>(sm + 4 * E + 2);
   if (warp < rows)
     route_token(logits, ldl, correction, idx, wts, nullptr, warp, E, groups, keep, top,
-                scratch + (size_t)warp * (2 * E + groups), lane);
+                scratch + (size_t)warp * (2 * E + groups), lane, rule);
   __threadfence_block();
   __syncthreads();   // the choices are written: the same block sorts them
   sort_pairs(idx, wts, rows * top, top, E, BM, max_tiles, src_row, row_w, pair_pos, tile_e, tile_r0, tile_n, sm);
@@ -538,8 +600,11 @@ CCB_API int ccb_moe_sort(const int* idx, const float* wts, int pairs, int top, i
 // ccb_moe_route and ccb_moe_sort in one kernel, for up to 32 tokens (no dense row of weights).
 CCB_API int ccb_moe_route_sort(const float* logits, int ldl, const float* correction, int* idx, float* wts, int rows,
                                int E, int groups, int keep, int top, int BM, int max_tiles, int* src_row, float* row_w,
-                               int* pair_pos, int* tile_e, int* tile_r0, int* tile_n, cudaStream_t stream) {
+                               int* pair_pos, int* tile_e, int* tile_r0, int* tile_n, int score_fn, int group_top,
+                               int renorm, float scale, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (score_fn < 0 || score_fn > 1 || group_top < 1 || group_top > 2) return CCB_REFUSE_ARG;
+  const RouteRule rule{score_fn, group_top, renorm ? 1 : 0, scale};
   if (rows > 32 || E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
       top > (E / groups) * keep || BM <= 0 || max_tiles < min(rows * top, (rows * top + BM - 1) / BM + E))
     return CCB_REFUSE_SIZE;
@@ -547,7 +612,7 @@ CCB_API int ccb_moe_route_sort(const float* logits, int ldl, const float* correc
   if (smem > 96 * 1024) return CCB_REFUSE_SIZE;
   cudaFuncSetAttribute(moe_route_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   ccb_launch(moe_route_sort_kernel, dim3(1), dim3(kSortThreads), smem, stream, logits, ldl, correction, idx, wts, rows,
-             E, groups, keep, top, BM, max_tiles, src_row, row_w, pair_pos, tile_e, tile_r0, tile_n);
+             E, groups, keep, top, BM, max_tiles, src_row, row_w, pair_pos, tile_e, tile_r0, tile_n, rule);
   return ccb_launch_status();
 }
 
@@ -613,6 +678,26 @@ CCB_API int ccb_moe_combine(void* out, const float* rows, const int* pair_pos, c
   else if (dtype == CCB_BF16)
     ccb_launch(moe_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out, rows,
                pair_pos, (const __nv_bfloat16*)shared, top, D, total);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}
+
+// act [rows, E F + shared] from gu [rows, 2 (E F + shared)] (gate columns, then up columns): see the kernel.
+CCB_API int ccb_moe_dense_glu_act(void* act, int lda, const void* gu, int ldg, const float* dense_w,
+                                  const float* shared_gate, int sg_stride, int rows, int E, int F, int shared,
+                                  int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (E < 0 || F <= 0 || shared < 0 || lda < E * F + shared || ldg < 2 * (E * F + shared)) return CCB_REFUSE_SIZE;
+  if (E > 0 && dense_w == nullptr) return CCB_REFUSE_ARG;
+  const size_t total = (size_t)rows * (E * F + shared);
+  const int blocks = (int)((total + 255) / 256 < 65535 * 8 ? (total + 255) / 256 : 65535 * 8);
+  if (dtype == CCB_F32)
+    ccb_launch(moe_dense_glu_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)act, lda, (const float*)gu,
+               ldg, dense_w, shared_gate, sg_stride, rows, E, F, shared);
+  else if (dtype == CCB_BF16)
+    ccb_launch(moe_dense_glu_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)act, lda,
+               (const __nv_bfloat16*)gu, ldg, dense_w, shared_gate, sg_stride, rows, E, F, shared);
   else
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();

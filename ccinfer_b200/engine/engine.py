@@ -103,6 +103,7 @@ class Engine:
             raise InvalidArgument("give kv_tokens or kv_memory_fraction, not both")
         group_keys: List[tuple] = []
         windows: List[Optional[int]] = []
+        chunks: List[Optional[int]] = []
         token_bytes: List[int] = []   # per group: bytes one token costs in all its layers
         owners: Dict[int, object] = {}  # run entry -> its CacheNeed
         self._entry_group: Dict[int, int] = {}
@@ -122,6 +123,7 @@ class Engine:
                 if need.group_key not in group_keys:
                     group_keys.append(need.group_key)
                     windows.append(need.window)
+                    chunks.append(getattr(need, "chunk", None))
                     token_bytes.append(0)
                 g = group_keys.index(need.group_key)
                 self._entry_group[i] = g
@@ -141,19 +143,22 @@ class Engine:
                 if e.cache_of not in self._entry_group:
                     raise InvalidArgument(f"order[{i}] reads the cache of entry {e.cache_of}, which keeps none")
                 self._entry_group[i] = self._entry_group[e.cache_of]
-        pages = self._pages_per_group(opt, group_keys, windows, token_bytes)
+        # how many of a request's latest tokens a group holds at most (None: all of them)
+        spans = [min(x for x in (w, c) if x is not None) if (w is not None or c is not None) else None
+                 for w, c in zip(windows, chunks)]
+        pages = self._pages_per_group(opt, group_keys, spans, token_bytes)
         for i, need in owners.items():
             n = pages[self._entry_group[i]]
             self._cache[i] = {t.name: torch.zeros((n,) + t.page_shape(P), dtype=t.dtype or self.dtype, device=rt.device)
                               for t in need.tensors}
         # the longest request: what the smallest pool of a group that keeps every token holds (a window group
         # gives pages back as a request moves on and bounds no length), and the model's own limit
-        all_keys = [n for n, w in zip(pages, windows) if w is None]
+        all_keys = [n for n, w in zip(pages, spans) if w is None]
         limit = (min(all_keys) if all_keys else self._base_pages(opt, P)) * P
         if plan.max_position is not None:
             limit = min(limit, plan.max_position)
         self.max_context = min(opt.max_context, limit) if opt.max_context else limit
-        self.cache = CacheManager([GroupSpec(k, w, P, n) for k, w, n in zip(group_keys, windows, pages)],
+        self.cache = CacheManager([GroupSpec(k, w, P, n, c) for k, w, n, c in zip(group_keys, windows, pages, chunks)],
                                   opt.max_requests, opt.max_tokens_per_step, self.max_context)
         self.graph_safe = all(getattr(p, "graph_safe", True) for p in plan.parts())
 

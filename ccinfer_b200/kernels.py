@@ -90,12 +90,23 @@ _SIGNATURES = {
                                  c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "ccb_latent_attention_mma_fits": [c_int, c_int],
     "ccb_moe_route": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_int, c_int, c_float, c_void_p],
+    "ccb_moe_dense_glu_act": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                              c_int, c_void_p],
+    "ccb_conv_rows": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
                       c_void_p],
+    "ccb_conv_state_rows": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                            c_void_p],
+    "ccb_attention_split_ex": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                               c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "ccb_moe_dense_act": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_moe_sort": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p, c_void_p, c_void_p],
     "ccb_moe_route_sort": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                           c_void_p],
     "ccb_moe_grouped": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_moe_gather_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -451,6 +462,44 @@ def conv_state_update(proj, offsets, conv_state, taps: int, cu_q, state_slot, n_
            "conv_state_update")
 
 
+def conv_rows(out, rows, w, taps: int, C: int, state, entry_of_token, cu_q, state_slot, n_entries: int,
+              values=None, status=None) -> None:
+    """A short causal convolution over time on the first ``C`` columns of a step's rows: out[t, c] = sum_j
+    w[c, j] * u[t - taps + 1 + j, c] over the request's rows in order, those before the step's first one taken from
+    ``state`` [slots, taps - 1, C] (compute type; zeros for a new request).  ``w`` float [C, taps], or None with
+    taps 1 for no convolution.  A request that brings one token has its state moved on here; for the others call
+    ``conv_state_rows`` afterwards.  ``values`` = (v_off, heads, head_size, real_size, v_first, lam): the columns
+    from v_off on are value heads of ``head_size`` coordinates of which ``real_size`` are real; with ``lam`` None
+    the results are also left in ``v_first`` [T, heads * real_size], else out = (1 - lam) out + lam v_first
+    (``lam`` a float tensor of one element)."""
+    _cuda(w, state, entry_of_token, cu_q, state_slot, status)
+    T = rows.shape[0]
+    assert rows.dtype == out.dtype and rows.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == T
+    assert w is None or (w.dtype == torch.float32 and w.shape == (C, taps))
+    assert state is None or (state.dtype == rows.dtype and tuple(state.shape[1:]) == (taps - 1, C))
+    vmode, v_off, vh, vhd, vd, v_first, lam = 0, 0, 0, 0, 0, None, None
+    if values is not None:
+        v_off, vh, vhd, vd, v_first, lam = values
+        vmode = 1 if lam is None else 2
+        _cuda(v_first, lam)
+        assert v_first.dtype == rows.dtype and v_first.shape[0] >= T and v_first[0].numel() == vh * vd
+        assert lam is None or (lam.dtype == torch.float32 and lam.numel() == 1)
+    _check(lib().ccb_conv_rows(_p(rows), rows.stride(0), _p(out), out.stride(0), _p(w), int(taps), int(C), _p(state),
+                               _p(entry_of_token), _p(cu_q), _p(state_slot), T, int(n_entries),
+                               state.shape[0] if state is not None else 0, int(v_off), int(vh), int(vhd), int(vd),
+                               _p(v_first), _p(lam), vmode, _dt(rows), _p(status), _stream()), "conv_rows")
+
+
+def conv_state_rows(rows, taps: int, C: int, state, cu_q, state_slot, entry0: int, n_entries: int) -> None:
+    """After ``conv_rows``: the last taps - 1 rows of every request among the entries entry0 .. entry0 + n_entries
+    - 1 that brought more than one token become its state."""
+    _cuda(state, cu_q, state_slot)
+    assert state.dtype == rows.dtype and rows.stride(1) == 1 and tuple(state.shape[1:]) == (taps - 1, C)
+    _check(lib().ccb_conv_state_rows(_p(rows), rows.stride(0), int(taps), int(C), _p(state), _p(cu_q), _p(state_slot),
+                                     int(entry0), int(n_entries), state.shape[0], _dt(rows), _stream()),
+           "conv_state_rows")
+
+
 def delta_recurrence(qn, kn, vv, gg, bb, state, out, cu_q, state_slot, n_entries: int, G: int, H: int, dk: int,
                      dv: int) -> None:
     """The gated delta rule over each request's tokens of the step, from and into ``state``
@@ -575,20 +624,59 @@ def latent_attention_mma(qa, cache, sink, gate, out, cu_q, pos0, entry_of_token,
         counters.own += 1   # the merge kernel
 
 
-def moe_route(logits, correction, idx, wts, dense_w, groups: int, keep: int) -> None:
-    """The router's choice per token from float logits [T, E]: softmax scores, + ``correction`` for the choice,
-    only experts of the ``keep`` best of ``groups`` groups of neighbours, the top idx.shape[1] of them.
-    idx int32 [T, top], wts float [T, top] (the chosen experts' scores, not renormalised), dense_w (optional)
-    float [T, E]: the same weights as a dense row."""
+class RouteRule:
+    """How a router turns logits into scores and weights.  ``score``: "softmax" over the experts or "sigmoid" of
+    each logit; ``group_top``: a group's score is the sum of this many of its largest choice scores (1 or 2);
+    ``renorm``: the chosen scores are divided by their sum (+ 1e-20); ``scale``: the weights' last factor."""
+
+    def __init__(self, score: str = "softmax", group_top: int = 1, renorm: bool = False, scale: float = 1.0):
+        if score not in ("softmax", "sigmoid") or group_top not in (1, 2):
+            raise Unsupported(f"router rule: score {score!r}, group_top {group_top}")
+        self.score, self.group_top, self.renorm, self.scale = score, int(group_top), bool(renorm), float(scale)
+
+    @property
+    def args(self):
+        return (1 if self.score == "sigmoid" else 0, self.group_top, 1 if self.renorm else 0, self.scale)
+
+
+_PLAIN_ROUTE = RouteRule()
+
+
+def moe_route(logits, correction, idx, wts, dense_w, groups: int, keep: int, rule: RouteRule = None,
+              E: int = None) -> None:
+    """The router's choice per token from float logits [T, E] (more columns may follow in a row): scores by
+    ``rule`` (default: softmax, not renormalised), + ``correction`` for the choice, only experts of the ``keep``
+    best of ``groups`` groups of neighbours, the top idx.shape[1] of them.  idx int32 [T, top], wts float [T, top]
+    (the chosen experts' weights), dense_w (optional) float [T, E]: the same weights as a dense row."""
     _cuda(correction, idx, wts, dense_w)
-    T, E = logits.shape
+    T = logits.shape[0]
+    if E is None:
+        E = dense_w.shape[1] if dense_w is not None else logits.shape[1]
+    assert logits.shape[1] >= E
     top = idx.shape[1]
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and idx.dtype == torch.int32
     assert idx.shape == (T, top) and wts.shape == (T, top) and wts.dtype == torch.float32 and idx.is_contiguous()
     assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
     assert dense_w is None or (dense_w.dtype == torch.float32 and dense_w.shape == (T, E))
     _check(lib().ccb_moe_route(_p(logits), logits.stride(0), _p(correction), _p(idx), _p(wts), _p(dense_w), T, E,
-                               int(groups), int(keep), top, _stream()), "moe_route")
+                               int(groups), int(keep), top, *(rule or _PLAIN_ROUTE).args, _stream()), "moe_route")
+
+
+def moe_dense_glu_act(act, gu, dense_w, E: int, F: int, shared: int, shared_gate=None) -> None:
+    """act [T, E F + shared] = silu(gate) * up * weight from the rows ``gu`` [T, 2 (E F + shared)] of ONE product
+    over all experts' gate rows and then all their up rows: weight = dense_w[t, e] for expert e's columns (exact
+    zeros where it was not chosen); the ``shared`` columns after them get sigmoid(shared_gate[t]) (``shared_gate``
+    a float column view [T], or None for 1)."""
+    _cuda(dense_w)
+    T = act.shape[0]
+    W = E * F + shared
+    assert act.stride(1) == 1 and gu.stride(1) == 1 and act.shape[1] == W and gu.shape == (T, 2 * W)
+    assert act.dtype == gu.dtype and (E == 0 or (dense_w.dtype == torch.float32 and dense_w.shape == (T, E)))
+    assert shared_gate is None or (shared_gate.dtype == torch.float32 and shared_gate.shape[0] == T
+                                   and shared_gate.dim() == 1)
+    _check(lib().ccb_moe_dense_glu_act(_p(act), act.stride(0), _p(gu), gu.stride(0), _p(dense_w), _p(shared_gate),
+                                       shared_gate.stride(0) if shared_gate is not None else 0, T, E, F, shared,
+                                       _dt(act), _stream()), "moe_dense_glu_act")
 
 
 def moe_dense_act(act, dense_w, E: int, F: int, shared: int) -> None:
@@ -624,20 +712,21 @@ MOE_ROUTE_SORT_MAX_TOKENS = 32
 
 
 def moe_route_sort(logits, correction, idx, wts, groups: int, keep: int, E: int, BM: int, src_row, row_w, pair_pos,
-                   tile_e, tile_r0, tile_n) -> None:
+                   tile_e, tile_r0, tile_n, rule: RouteRule = None) -> None:
     """``moe_route`` (without the dense row) and ``moe_sort`` as one kernel, for steps of up to
     MOE_ROUTE_SORT_MAX_TOKENS tokens."""
     _cuda(correction, idx, wts, src_row, row_w, pair_pos, tile_e, tile_r0, tile_n)
     T, top = idx.shape
     n_tiles = tile_e.numel()
-    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape == (T, E)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[0] == T and logits.shape[1] >= E
     assert idx.dtype == torch.int32 and idx.is_contiguous() and wts.dtype == torch.float32 and wts.shape == (T, top)
     assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
     assert src_row.numel() >= T * top and row_w.numel() >= T * top and pair_pos.numel() >= T * top
     assert tile_r0.numel() >= n_tiles and tile_n.numel() >= n_tiles and n_tiles >= moe_max_tiles(T * top, E, BM)
     _check(lib().ccb_moe_route_sort(_p(logits), logits.stride(0), _p(correction), _p(idx), _p(wts), T, E, int(groups),
                                     int(keep), top, BM, n_tiles, _p(src_row), _p(row_w), _p(pair_pos), _p(tile_e),
-                                    _p(tile_r0), _p(tile_n), _stream()), "moe_route_sort")
+                                    _p(tile_r0), _p(tile_n), *(rule or _PLAIN_ROUTE).args, _stream()),
+           "moe_route_sort")
 
 
 def moe_grouped(c, a, src_row, w, w_expert_stride: int, row_w, tile_e, tile_r0, tile_n, N: int, K: int, BM: int,
@@ -797,11 +886,17 @@ def attention_split_plan(n_rows: int, nq: int, nkv: int, hd: int, heads_per_bloc
 
 def attention_split(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
                     n_entries: int, row0: int, n_rows: int, window: int, scale: float, num_splits: int,
-                    status=None) -> None:
+                    status=None, chunk: int = 0, sink=None, gate=None) -> None:
     """Attention of the token rows row0 .. row0 + n_rows - 1, each a single query with its own position
     and request; the key range is cut into ``num_splits`` pieces merged afterwards (scratch from
-    ``attention_split_plan``; unused with one split)."""
-    _cuda(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table, status)
+    ``attention_split_plan``; unused with one split).  ``chunk`` > 0: a query sees only the keys of its own run of
+    ``chunk`` positions (counted from the sequence's start); ``sink`` float [nq]: one more term exp(sink[h]) in
+    every softmax denominator of head h; ``gate`` [T, >= nq] (compute type, a view with unit column stride): head
+    h's result times sigmoid(gate[t, h])."""
+    _cuda(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table, status, sink)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == q.shape[1])
+    assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1 and gate.shape[0] == q.shape[0]
+                            and gate.shape[1] >= q.shape[1])
     T, nq, hd = q.shape
     num_pages, nkv, page_size, hd2 = k_cache.shape
     assert hd2 == hd and out.shape == q.shape and q.dtype == k_cache.dtype == v_cache.dtype == out.dtype
@@ -809,10 +904,12 @@ def attention_split(q, k_cache, v_cache, out, part_acc, part_ml, positions, entr
     if num_splits > 1:
         assert part_acc.dtype == part_ml.dtype == torch.float32
         assert part_acc.numel() >= n_rows * nq * num_splits * hd and part_ml.numel() >= n_rows * nq * num_splits * 2
-    _check(lib().ccb_attention_split(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_acc), _p(part_ml),
-                                     _p(positions), _p(entry_of_token), _p(block_table), block_table.stride(0),
-                                     n_entries, row0, n_rows, nq, nkv, hd, page_size, num_pages, int(window),
-                                     float(scale), num_splits, _dt(q), _p(status), _stream()), "attention_split")
+    _check(lib().ccb_attention_split_ex(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_acc), _p(part_ml),
+                                        _p(positions), _p(entry_of_token), _p(block_table), block_table.stride(0),
+                                        n_entries, row0, n_rows, nq, nkv, hd, page_size, num_pages, int(window),
+                                        float(scale), num_splits, int(chunk), _p(sink), _p(gate),
+                                        gate.stride(0) if gate is not None else 0, _dt(q), _p(status), _stream()),
+           "attention_split")
     if num_splits > 1:
         counters.own += 1  # the merge kernel
 

@@ -32,7 +32,7 @@ ERRORS = {1: InvalidArgument, 2: KVBlockExhausted, 3: KVBlockDoubleFree, 4: KVIn
 
 
 class Group(Structure):
-    _fields_ = [("window", c_int), ("page_size", c_int), ("num_pages", c_int)]
+    _fields_ = [("window", c_int), ("page_size", c_int), ("num_pages", c_int), ("chunk", c_int)]
 
 
 class Options(Structure):
@@ -172,10 +172,11 @@ class HostCore:
     """One engine of the host core.  Sequences are named by 64-bit integers."""
 
     def __init__(self, groups, max_seqs: int, max_tokens_per_step: int, max_context: int):
-        """``groups``: (window or None, page_size, num_pages) per cache group."""
+        """``groups``: (window or None, page_size, num_pages[, chunk or None]) per cache group."""
         self._lib = lib()
         self.n_groups = len(groups)
-        arr = (Group * max(1, self.n_groups))(*[Group(int(w or 0), int(p), int(n)) for w, p, n in groups])
+        arr = (Group * max(1, self.n_groups))(*[Group(int(g[0] or 0), int(g[1]), int(g[2]), int(g[3] or 0) if len(g) > 3 else 0)
+                                                  for g in groups])
         opt = Options(self.n_groups, arr, int(max_seqs), int(max_tokens_per_step), int(max_context))
         self._h = c_void_p()
         rc = self._lib.ccinfer_create(byref(opt), byref(self._h))

@@ -72,21 +72,28 @@ class CacheNeed:
 
     ``window`` None: a query may read every earlier token, pages live as long as
     the request.  ``window`` W: a query at position p reads tokens p-W+1 .. p;
-    pages wholly before that are given back while the request runs.  Layers
-    with equal (window) share a page pool and block tables (a cache group);
-    each layer has its own tensors of its own geometry.
+    pages wholly before that are given back while the request runs.  ``chunk``
+    C: a query at position p reads the tokens from floor(p / C) * C on (runs of
+    C positions counted from the sequence's start); pages wholly before the run
+    of the next token are given back.  Layers with equal (window, chunk) share a
+    page pool and block tables (a cache group); each layer has its own tensors
+    of its own geometry.
     """
     tensors: Tuple[CachedTensor, ...]
     window: Optional[int] = None
+    chunk: Optional[int] = None
 
     @classmethod
-    def keys_and_values(cls, kv_heads: int, head_dim: int, window: Optional[int] = None) -> "CacheNeed":
+    def keys_and_values(cls, kv_heads: int, head_dim: int, window: Optional[int] = None,
+                        chunk: Optional[int] = None) -> "CacheNeed":
         """Keys "k" and values "v" of an attention layer: [pages, kv_heads, page_size, head_dim] each."""
         shape = (int(kv_heads), int(head_dim))
-        return cls((CachedTensor("k", shape, token_axis=1), CachedTensor("v", shape, token_axis=1)), window)
+        return cls((CachedTensor("k", shape, token_axis=1), CachedTensor("v", shape, token_axis=1)), window, chunk)
 
     @property
     def group_key(self):
+        if self.chunk is not None:
+            return ("chunk", self.chunk) if self.window is None else ("window+chunk", self.window, self.chunk)
         return ("window", self.window) if self.window is not None else ("all",)
 
     def bytes_per_token(self, compute_dtype: torch.dtype) -> int:

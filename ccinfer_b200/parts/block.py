@@ -18,20 +18,36 @@ from .base import Block, FeedForward, Mixer, Norm, Residual, ResidualSink
 
 
 class PreNormBlock(Block):
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward):
-        self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+    """h += Mixer(norm1(h)); h += FeedForward(norm2(h)); optionally, last, h += side(h, token).
+
+    The feed-forward (with norm2) may be absent.  ``side`` (``parts.embedding.TokenSideInput``): the block's last
+    sum also writes the stream's rows in the compute type for the side input's gate, and the side input's own sum
+    (with its RMS norm) writes the first norm of the block that follows (``stream.ready``)."""
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm] = None, ffn: Optional[FeedForward] = None,
+                 side=None):
+        if (ffn is None) != (norm2 is None):
+            raise ValueError("a feed-forward comes with its norm, or neither is given")
+        self.norm1, self.mixer, self.norm2, self.ffn, self.side = norm1, mixer, norm2, ffn, side
+        self.rt = None
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn, self.side) if p is not None]
 
     @property
     def graph_safe(self):
-        return all(p.graph_safe for p in (self.norm1, self.mixer, self.norm2, self.ffn))
+        return all(p.graph_safe for p in self._parts())
 
     def tensor_specs(self):
-        return (self.norm1.tensor_specs() + self.mixer.tensor_specs() + self.norm2.tensor_specs()
-                + self.ffn.tensor_specs())
+        return [s for p in self._parts() for s in p.tensor_specs()]
 
     def bind(self, rt, fetch):
-        for p in (self.norm1, self.mixer, self.norm2, self.ffn):
+        self.rt = rt
+        for p in self._parts():
             p.bind(rt, fetch)
+        self._ones = None
+        if self.side is not None:   # the plain sum as the kernel that sums with a factor per channel
+            self._ones = torch.ones(self.side.hidden, dtype=torch.float32, device=rt.device)
 
     @property
     def first_norm(self):
@@ -39,16 +55,41 @@ class PreNormBlock(Block):
 
     def forward(self, stream: Residual, step, cache, state) -> None:
         after = stream.next_norm                     # the norm that the block after this one starts with
+        if self.side is not None:
+            after = None                             # (the side input's sum writes that norm's rows itself)
         stream.takes_unscaled = self.mixer.takes_unscaled
         x = self.norm1.fold(stream)
-        step.residual_sink = ResidualSink(stream, self.norm2)
+        nxt = self.norm2 if self.ffn is not None else after
+        step.residual_sink = ResidualSink(stream, nxt) if nxt is not None else None
         stream.pending = self.mixer.forward(x, step, cache, state)
-        stream.takes_unscaled = self.ffn.takes_unscaled
-        x = self.norm2.fold(stream)
-        step.residual_sink = ResidualSink(stream, after) if after is not None else None
-        stream.pending = self.ffn.forward(x, step)
+        if self.ffn is not None:
+            stream.takes_unscaled = self.ffn.takes_unscaled
+            x = self.norm2.fold(stream)
+            step.residual_sink = ResidualSink(stream, after) if after is not None else None
+            stream.pending = self.ffn.forward(x, step)
         step.residual_sink = None
         stream.takes_unscaled = False
+        if self.side is not None:
+            self._side(stream, step)
+
+    def _side(self, stream: Residual, step) -> None:
+        """h += pending, then h += side(h, token) with the side input's norm, in two kernels that also write what
+        reads the stream next (the stream's rows for the side input's gate; the next block's first norm)."""
+        rt = self.rt
+        T, D = stream.h.shape
+        after = stream.next_norm
+        rows = rt.scratch.get("stream_rows", (rt.max_tokens, D), rt.dtype)[:T]
+        delta, stream.pending = stream.pending, None
+        if delta is None:
+            raise RuntimeError("the block's last part left nothing to add where a side input follows")
+        stream.unscaled = stream.ready = None
+        kernels.scaled_residual(stream.h, rt.rows(delta), self._ones, y=rows)
+        y = self.side.forward(rows, step)
+        usable = after is not None and hasattr(after, "w") and hasattr(after, "eps")
+        x = rt.scratch.get(after.scratch_key, (rt.max_tokens, D), rt.dtype)[:T] if usable else None
+        kernels.postnorm_residual(stream.h, rt.rows(y), self.side.w, 1.0, self.side.eps, y=x,
+                                  w_next=after.w if usable else None, eps_next=after.eps if usable else 0.0)
+        stream.ready = (after, x) if usable else None
 
 
 class SandwichNormBlock(Block):

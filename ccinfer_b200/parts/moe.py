@@ -5,7 +5,11 @@
     best choice score can be chosen; the ``top`` largest c are chosen; their weights are their s, as they are
     m = sum_chosen s_e * Wdown_e act(Wup_e x)  +  Wdown_s act(Wup_s x)      (a shared expert for every token)
 
-``activation`` "relu2": act(u) = relu(u)^2.  No biases.
+``activation`` "relu2": act(u) = relu(u)^2.  No biases.  ``activation`` "swiglu": every expert (the shared one
+too) has a gate matrix beside its up matrix, act = silu(Wgate_e x) * (Wup_e x).  ``rule`` (``kernels.RouteRule``)
+says how logits become scores and weights (sigmoid scores, a group's score as the sum of its two best, chosen
+scores renormalised, a last factor); ``names["shared_gate"]``: the shared expert's result is multiplied by
+sigmoid(w_sg . x), one number per token (the row rides along as one more row of the router's matrix).
 
 Two forms, chosen by size (``sparse=`` forces one):
 
@@ -40,11 +44,14 @@ class MixtureOfExperts(FeedForward):
     TC_MIN_ROWS_PER_EXPERT = 8
 
     def __init__(self, hidden: int, experts: int, top: int, expert_ff: int, names: dict, groups: int = 1,
-                 keep: int = 1, shared_ff: int = 0, activation: str = "relu2", sparse=None):
-        """``names``: "router", "correction" (optional), "up" and "down" with ``{e}`` for the expert's number,
-        "shared_up" / "shared_down" (with ``shared_ff`` > 0)."""
-        if activation != "relu2":
+                 keep: int = 1, shared_ff: int = 0, activation: str = "relu2", sparse=None, rule=None):
+        """``names``: "router", "correction" (optional), "up" and "down" (and "gate" with "swiglu") with ``{e}`` for
+        the expert's number, "shared_up" / "shared_down" (/ "shared_gate_proj") with ``shared_ff`` > 0,
+        "shared_gate" (optional)."""
+        if activation not in ("relu2", "swiglu"):
             raise Unsupported(f"expert activation {activation!r}")
+        self.glu = activation == "swiglu"
+        self.rule = rule
         if experts % groups or not (0 < keep <= groups) or not (0 < top <= (experts // groups) * keep):
             raise Unsupported(f"{experts} experts in {groups} groups of which {keep} are kept cannot give {top}")
         self.hidden, self.E, self.top, self.F = int(hidden), int(experts), int(top), int(expert_ff)
@@ -60,15 +67,26 @@ class MixtureOfExperts(FeedForward):
         if n.get("correction"):
             specs.append(TensorSpec(n["correction"], (self.E,), role="vector"))
         for e in range(self.E):
+            if self.glu:
+                specs.append(TensorSpec(n["gate"].format(e=e), (self.F, D)))
             specs += [TensorSpec(n["up"].format(e=e), (self.F, D)), TensorSpec(n["down"].format(e=e), (D, self.F))]
         if self.SF:
+            if self.glu:
+                specs.append(TensorSpec(n["shared_gate_proj"], (self.SF, D)))
             specs += [TensorSpec(n["shared_up"], (self.SF, D)), TensorSpec(n["shared_down"], (D, self.SF))]
+            if n.get("shared_gate"):
+                specs.append(TensorSpec(n["shared_gate"], (1, D)))
         return specs
 
     def bind(self, rt, fetch):
         self.rt = rt
         n = self.names
         self.w_router = fetch(n["router"])
+        self.has_shared_gate = bool(self.SF and n.get("shared_gate"))
+        if self.has_shared_gate:   # its logit is column E of the router's product
+            self.w_router = torch.cat([self.w_router, fetch(n["shared_gate"]).view(1, -1)], dim=0).contiguous()
+        if self.glu:
+            return self._bind_glu(rt, fetch)
         self.correction = fetch(n["correction"]).float().contiguous() if n.get("correction") else None
         ups = [fetch(n["up"].format(e=e)) for e in range(self.E)]
         downs = [fetch(n["down"].format(e=e)) for e in range(self.E)]
@@ -85,20 +103,57 @@ class MixtureOfExperts(FeedForward):
         self.w_up = torch.cat(ups, dim=0).contiguous()        # [E F (+ SF), D]
         self.w_down = torch.cat(downs, dim=1).contiguous()    # [D, E F (+ SF)]
 
+    def _bind_glu(self, rt, fetch):
+        """The gated form.  Dense: ONE matrix of all gate rows (the experts', then the shared expert's) followed by
+        all up rows in the same order, and all second matrices side by side."""
+        n = self.names
+        self.correction = fetch(n["correction"]).float().contiguous() if n.get("correction") else None
+        gates = [fetch(n["gate"].format(e=e)) for e in range(self.E)]
+        ups = [fetch(n["up"].format(e=e)) for e in range(self.E)]
+        downs = [fetch(n["down"].format(e=e)) for e in range(self.E)]
+        fits = rt.dtype == torch.float32 or (self.hidden % 8 == 0 and self.F % 8 == 0)
+        big = 3 * self.E * self.F * self.hidden >= self.SPARSE_MIN_WEIGHTS
+        self.use_sparse = fits and (big if self.sparse is None else bool(self.sparse))
+        self.w_shared_up = self.w_shared_down = None
+        if self.use_sparse:
+            # every expert's gate and up rows in turn (row 2 f its gate f, row 2 f + 1 its up f): a thread of the
+            # grouped product holds both and the activation is its epilogue
+            self.w_up = torch.stack([torch.stack([g, u], dim=1).reshape(2 * self.F, -1) for g, u in zip(gates, ups)]
+                                    ).reshape(self.E * 2 * self.F, -1).contiguous()
+            self.w_down = torch.cat(downs, dim=1).contiguous()
+            if self.SF:
+                self.w_shared_up = torch.cat([fetch(n["shared_gate_proj"]), fetch(n["shared_up"])], dim=0).contiguous()
+                self.w_shared_down = fetch(n["shared_down"])
+            return
+        if self.SF:
+            gates.append(fetch(n["shared_gate_proj"]))
+            ups.append(fetch(n["shared_up"]))
+            downs.append(fetch(n["shared_down"]))
+        self.w_up = torch.cat(gates + ups, dim=0).contiguous()       # [2 (E F + SF), D]
+        self.w_down = torch.cat(downs, dim=1).contiguous()           # [D, E F + SF]
+
+    def _shared_gate(self, T):
+        """The float column of the shared expert's gate logits in the router's product, or None."""
+        if not self.has_shared_gate:
+            return None
+        rt = self.rt
+        return rt.scratch.get("moe_logits", (rt.max_tokens, self.w_router.shape[0]), torch.float32)[:T, self.E]
+
     def route(self, x, T, sort_into=None):
         """idx int32 [T, top], wts float [T, top], dense float [T, E] for the rows of x.  ``sort_into`` (BM and the
         arrays of ``kernels.moe_sort``): the pairs are sorted by expert as well, in the same kernel where the step
         has few tokens (then there is no dense row)."""
         rt = self.rt
-        logits = rt.scratch.get("moe_logits", (rt.max_tokens, self.E), torch.float32)[:T]
+        logits = rt.scratch.get("moe_logits", (rt.max_tokens, self.w_router.shape[0]), torch.float32)[:T]
         rt.linear(logits, x, self.w_router)
         idx = rt.scratch.get("moe_idx", (rt.max_tokens, self.top), torch.int32)[:T]
         wts = rt.scratch.get("moe_wts", (rt.max_tokens, self.top), torch.float32)[:T]
         if sort_into is not None and T <= kernels.MOE_ROUTE_SORT_MAX_TOKENS:
-            kernels.moe_route_sort(logits, self.correction, idx, wts, self.groups, self.keep, self.E, *sort_into)
+            kernels.moe_route_sort(logits, self.correction, idx, wts, self.groups, self.keep, self.E, *sort_into,
+                                   rule=self.rule)
             return idx, wts, None
         dense = rt.scratch.get("moe_dense", (rt.max_tokens, self.E), torch.float32)[:T]
-        kernels.moe_route(logits, self.correction, idx, wts, dense, self.groups, self.keep)
+        kernels.moe_route(logits, self.correction, idx, wts, dense, self.groups, self.keep, rule=self.rule, E=self.E)
         if sort_into is not None:
             kernels.moe_sort(idx, wts, self.E, *sort_into)
         return idx, wts, dense
@@ -150,7 +205,12 @@ class MixtureOfExperts(FeedForward):
             return self._forward_sparse(x, T)
         _, _, dense = self.route(x, T)
         act = rt.scratch.get("moe_act", (rt.max_tokens, self.width), rt.dtype)[:T]
-        rt.linear(act, x, self.w_up)
-        kernels.moe_dense_act(act, dense, self.E, self.F, self.SF)
+        if self.glu:
+            gu = rt.scratch.get("moe_gate_up", (rt.max_tokens, 2 * self.width), rt.dtype)[:T]
+            rt.linear(gu, x, self.w_up)
+            kernels.moe_dense_glu_act(act, gu, dense, self.E, self.F, self.SF, self._shared_gate(T))
+        else:
+            rt.linear(act, x, self.w_up)
+            kernels.moe_dense_act(act, dense, self.E, self.F, self.SF)
         out = rt.scratch.get("ffn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
         return rt.linear(out, act, self.w_down)

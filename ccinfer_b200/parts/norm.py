@@ -8,9 +8,13 @@ from .base import Norm, Residual, TensorSpec, UnscaledRows
 
 
 class RMSNorm(Norm):
-    def __init__(self, dim: int, eps: float, weight_name: str, scratch_key: str = "normed", weight_offset: float = 0.0):
+    def __init__(self, dim: int, eps: float, weight_name: str, scratch_key: str = "normed", weight_offset: float = 0.0,
+                 weight_scale: float = 1.0):
         """``weight_offset`` c: the stored weight lies around zero and the norm multiplies by (c + w); the sum is
-        made once, in float, when the weight is bound (exact for a bfloat16 w of ordinary size)."""
+        made once, in float, when the weight is bound (exact for a bfloat16 w of ordinary size).
+        ``weight_scale`` s: the norm's rows times s (a constant factor on what a product makes of them, a
+        model's scale on its logits for instance, costs nothing here)."""
+        self.weight_scale = float(weight_scale)
         self.dim, self.eps, self.weight_name, self.scratch_key = int(dim), float(eps), weight_name, scratch_key
         self.weight_offset = float(weight_offset)
         self.w = None
@@ -25,6 +29,8 @@ class RMSNorm(Norm):
         self.w = fetch(self.weight_name)
         if self.weight_offset:
             self.w = (self.w.float() + self.weight_offset).contiguous()
+        if self.weight_scale != 1.0:
+            self.w = (self.w.float() * self.weight_scale).contiguous()
 
     def fold(self, stream: Residual, rows=None, n_rows=None):
         rt = self.rt

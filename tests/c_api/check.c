@@ -49,7 +49,7 @@ static int read_hook(void* user, int64_t ticket, int n, int* tokens_out) {
 }
 
 int main(void) {
-  ccinfer_group groups[2] = {{0, 4, 14}, {6, 4, 14}};   /* all keys; a window of six */
+  ccinfer_group groups[2] = {{0, 4, 14, 0}, {6, 4, 14, 0}};   /* all keys; a window of six */
   ccinfer_options opt = {2, groups, 4, 32, 64};
   CHECK(ccinfer_create(&opt, &g_engine));
   ccinfer_scheduler_options so = {8, 32, 4, 64, -1, 0};
