@@ -35,10 +35,10 @@ runs one of the two other workloads of the reference's benchmark record through 
 continuous batch at the Qwen3-14B shape; four 16,384-token prompts at the Qwen3-32B shape) and prints a
 line of its own: output tokens a second, the distribution of the step calls, the pages' high water.
 
-    python bench.py --design tugelorn|dufizen [--design-sizes mid,8b] [--layers L] [--design-profile]
+    python bench.py --design tugelorn|dufizen|burolorn [--design-sizes mid,8b] [--layers L] [--design-profile]
 
 measures another design of the package beside its closest model (Tugelorn beside Qwen3, Dufizen beside
-Tugelorn) at equal layer sizes (same width, heads, head size,
+Tugelorn, Burolorn beside Qwen3) at equal layer sizes (same width, heads, head size,
 intermediate size, vocabulary and number of layers; random weights): one prompt of 2,048 and of 8,192 tokens
 in steps of 2,048 (tokens a second) and decode steps of 1 and 8 requests after 2,048-token prompts, replayed
 from CUDA graphs (tokens a second), one JSON line per size.  With --design-profile it only runs a prompt and a
@@ -316,6 +316,24 @@ def dufizen_config(size: str, layers: int):
     return DufizenConfig.from_json(j)
 
 
+def burolorn_config(size: str, layers: int):
+    """Every layer: attention with a convolution of four taps on q, k and v, head norms, half of each head
+    rotated, runs of 1,024 positions as the mask, a sink, values mixed with the first layer's, a gate per head; the
+    feed-forward in turn dense (F) and a mixture of 32 gated experts of F / 8 of which 4 are used plus a shared one
+    of F / 2 (F intermediate channels per token either way); a token side input of 256 columns."""
+    from ccinfer_b200.config.burolorn import BurolornConfig
+    D, H, G, hd, F, V = DESIGN_SIZES[size]
+    mixer = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "conv": 4, "v_mix": True,
+             "mask": {"size": 1024}, "rot": {"dims": hd // 2, "base": 1000000.0}}
+    mlps = [{"kind": "dense", "ff": F},
+            {"kind": "moe", "expert": {"ff": F // 8}, "shared": {"ff": F // 2},
+             "router": {"experts": 32, "top": 4, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}]
+    j = {"architecture": "Burolorn", "vocab": V, "width": D, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+         "token_side": {"dim": 256},
+         "layers": [{"type": "attention", "mixer": mixer, "mlp": mlps[i % 2]} for i in range(layers)]}
+    return BurolornConfig.from_json(j)
+
+
 def run_design(args) -> int:
     import numpy as np
     import torch
@@ -324,7 +342,8 @@ def run_design(args) -> int:
     from ccinfer_b200.engine.engine import Engine, EngineOptions, StepEntry
 
     # design -> (its configuration at a size, the closest model it is measured beside)
-    designs = {"tugelorn": (tugelorn_config, "qwen3"), "dufizen": (dufizen_config, "tugelorn")}
+    designs = {"tugelorn": (tugelorn_config, "qwen3"), "dufizen": (dufizen_config, "tugelorn"),
+               "burolorn": (burolorn_config, "qwen3")}
     if args.design not in designs:
         print(json.dumps({"error": f"unknown design {args.design!r}"}))
         return 2
@@ -442,7 +461,7 @@ def main() -> int:
     ap.add_argument("--shape", default="8b", choices=["8b", "14b", "32b"], help="layer shape of --profile-steps")
     ap.add_argument("--workload", default="decode", choices=["decode", "mix14b", "long32b"],
                     help="decode (the default line) or one of the two other workloads of the benchmark record")
-    ap.add_argument("--design", default=None, help="tugelorn (beside Qwen3) or dufizen (beside Tugelorn): that design beside its closest model at "
+    ap.add_argument("--design", default=None, help="tugelorn (beside Qwen3), dufizen (beside Tugelorn) or burolorn (beside Qwen3): that design beside its closest model at "
                                                    "equal layer sizes")
     ap.add_argument("--design-sizes", default="mid,8b", help="layer sizes of --design: " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--design-profile", action="store_true", help="with --design: a prompt and four eager decode steps")

@@ -73,6 +73,10 @@ def main(argv=None) -> int:
     ap.add_argument("--stats", action="store_true", help="print cache and scheduler figures to stderr")
     ap.add_argument("--write-random-model", metavar="CONFIG_JSON",
                     help="write a random model folder to --model-path from this config.json and exit")
+    ap.add_argument("--store-dtype", default=None, choices=["bfloat16", "float32"],
+                    help="with --write-random-model: the type the file holds (default: the configuration's, else "
+                         "bfloat16; float32 keeps the drawn values unrounded, as --random-config --dtype float32 uses "
+                         "them)")
     ap.add_argument("--random-config", metavar="CONFIG_JSON",
                     help="instead of --model-path: a model of this config.json with random weights (--weights-seed, "
                          "--weights-std) drawn on the device")
@@ -96,7 +100,7 @@ def main(argv=None) -> int:
             with open(args.write_random_model) as f:
                 cj = json.load(f)
             cfg = architecture_of(cj).parse_config(cj)
-            write_random_model(args.model_path, cfg, args.weights_seed, args.weights_std)
+            write_random_model(args.model_path, cfg, args.weights_seed, args.weights_std, args.store_dtype)
             print(f"wrote {args.model_path}", file=sys.stderr)
             return 0
         if args.dump_config:

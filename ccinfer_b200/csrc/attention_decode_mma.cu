@@ -28,7 +28,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                             const int* __restrict__ positions, const int* __restrict__ entry_of_token,
                             const int* __restrict__ block_table, int bt_stride, int n_entries, int row0, int nq,
                             int nkv, int page_size, int num_pages, int window, float scale, int num_splits,
-                            int* status) {
+                            AttnExtra ex, int* status) {
   ccb::pdl_begin();
   constexpr int CH = HD / 8;            // 16-byte chunks per row
   constexpr int KS = HD / 16;           // k steps of q.k, and pairs of 8-wide output blocks of P v
@@ -74,7 +74,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     }
     const int* bt = block_table + (size_t)b * bt_stride;
     const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
-    const int j0 = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int j0 = first_visible_key(p, window, ex.chunk);
     const int first_tile = j0 / kTileKeys, last_tile = p / kTileKeys;
     const int n_tiles = last_tile - first_tile + 1;
     const int per_split = (n_tiles + num_splits - 1) / num_splits;
@@ -242,6 +242,8 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     }
     const int h = h0 + row;
     if (num_splits == 1) {
+      a *= attn_sink_fold(ex, h, mm, ll);
+      if (mm != -CUDART_INF_F) a *= attn_gate<__nv_bfloat16>(ex, t, h);
       out[((size_t)t * nq + h) * HD + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
     } else {
       const size_t slot = ((size_t)r * nq + h) * num_splits + split;
@@ -256,7 +258,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
 
 __global__ void attention_merge_bf16_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_acc,
                                             const float* __restrict__ part_ml, int row0, int nq, int hd,
-                                            int num_splits) {
+                                            int num_splits, AttnExtra ex) {
   ccb::pdl_begin();
   const int r = blockIdx.x, h = blockIdx.y;
   const size_t base = ((size_t)r * nq + h) * num_splits;
@@ -269,10 +271,11 @@ __global__ void attention_merge_bf16_kernel(__nv_bfloat16* __restrict__ out, con
   }
   float ll = 0.f;
   for (int s = 0; s < num_splits; ++s) ll += part_ml[(base + s) * 2 + 1] * __expf(part_ml[(base + s) * 2] - mm);
+  const float fold = attn_sink_fold(ex, h, mm, ll) * attn_gate<__nv_bfloat16>(ex, row0 + r, h);
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float a = 0.f;
     for (int s = 0; s < num_splits; ++s) a += part_acc[(base + s) * hd + d] * __expf(part_ml[(base + s) * 2] - mm);
-    o[d] = __float2bfloat16_rn(a / ll);
+    o[d] = __float2bfloat16_rn(a * fold / ll);
   }
 }
 
@@ -280,7 +283,7 @@ template <int HD>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_acc, float* part_ml,
            const int* positions, const int* entry_of_token, const int* block_table, int bt_stride, int n_entries,
            int row0, int n_rows, int nq, int nkv, int page_size, int num_pages, int window, float scale,
-           int num_splits, int* status, cudaStream_t stream) {
+           int num_splits, AttnExtra ex, int* status, cudaStream_t stream) {
   const int G = nq / nkv, gchunks = (G + 15) / 16;
   const size_t smem = (size_t)2 * kStages * kTileKeys * HD * sizeof(__nv_bfloat16);
   static bool configured = false;  // per process and head size; the attribute belongs to the function
@@ -294,25 +297,29 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
   ccb_launch(attention_decode_mma_kernel<HD>, grid, kThreads, smem, stream, 
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
       part_acc, part_ml, positions, entry_of_token, block_table, bt_stride, n_entries, row0, nq, nkv, page_size,
-      num_pages, window, scale, num_splits, status);
+      num_pages, window, scale, num_splits, ex, status);
   int rc = ccb_launch_status();
   if (rc != 0 || num_splits == 1) return rc;
   ccb_launch(attention_merge_bf16_kernel, dim3(n_rows, nq), 128, 0, stream, (__nv_bfloat16*)out, part_acc, part_ml, row0,
-                                                                     nq, HD, num_splits);
+                                                                     nq, HD, num_splits, ex);
   return ccb_launch_status();
 }
 
 }  // namespace
 
 // bfloat16 only, head size 64 or 128 (others: CCB_REFUSE_SIZE, use ccb_attention_split).  Scratch as for
-// ccb_attention_split: n_rows * nq * num_splits * (hd + 2) floats, unused with one split.
+// ccb_attention_split: n_rows * nq * num_splits * (hd + 2) floats, unused with one split.  chunk, sink, gate,
+// gate_stride: see AttnExtra (0 / null: none).
 CCB_API int ccb_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
                                      float* part_acc, float* part_ml, const int* positions,
                                      const int* entry_of_token, const int* block_table, int bt_stride,
                                      int n_entries, int row0, int n_rows, int nq, int nkv, int hd, int page_size,
-                                     int num_pages, int window, float scale, int num_splits, int* status,
+                                     int num_pages, int window, float scale, int num_splits, int chunk,
+                                     const float* sink, const void* gate, int gate_stride, int* status,
                                      cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (chunk < 0 || (gate != nullptr && gate_stride < nq)) return CCB_REFUSE_ARG;
+  const AttnExtra ex{chunk, sink, gate, gate_stride};
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || bt_stride <= 0 || num_splits <= 0 ||
       num_splits > 64)
     return CCB_REFUSE_SIZE;
@@ -320,10 +327,10 @@ CCB_API int ccb_attention_decode_mma(const void* q, const void* k_cache, const v
   if (hd == 128)
     return launch<128>(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
                        bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window, scale, num_splits,
-                       status, stream);
+                       ex, status, stream);
   if (hd == 64)
     return launch<64>(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
                       bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window, scale, num_splits,
-                      status, stream);
+                      ex, status, stream);
   return CCB_REFUSE_SIZE;
 }

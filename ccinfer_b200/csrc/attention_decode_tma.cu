@@ -69,7 +69,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                             const int* __restrict__ positions, const int* __restrict__ entry_of_token,
                             const int* __restrict__ block_table, int bt_stride, int n_entries, int row0, int nq,
                             int nkv, int page_size, int page_shift, int num_pages, int window, float scale,
-                            int num_splits, int* __restrict__ counters, int* status) {
+                            int num_splits, int* __restrict__ counters, AttnExtra ex, int* status) {
   // The kernel after this one is let in only when this one ends: a product that came in while the last
   // blocks were still merging made the pair slower (measured), not faster.
   // The fused form may itself come in early (programmatic dependent launch): the cached keys and values it
@@ -110,7 +110,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   // others have nothing to do (the grid is sized without knowing the context).  Where the last block
   // merges, they leave at once and are not waited for (measured at one row and 2,048 keys with a grid of
   // 32 splits: 12.1 us when all 32 took a tile and were merged, as against 10.6 us with a grid of 8).
-  const int j0 = (!padded && window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int j0 = padded ? 0 : first_visible_key(p, window, ex.chunk);
   const int first_tile = j0 / kTileKeys, last_tile = (padded ? 0 : p) / kTileKeys;
   const int n_tiles = last_tile - first_tile + 1;
   const int eff_splits = padded ? 1 : min(num_splits, max(1, (n_tiles + kMinSplitTiles - 1) / kMinSplitTiles));
@@ -466,6 +466,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     }
     const int h = h0 + row;
     if (num_splits == 1) {
+      a *= attn_sink_fold(ex, h, mm, ll);
+      if (!padded) a *= attn_gate<__nv_bfloat16>(ex, t, h);
       out[((size_t)t * nq + h) * HD + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
     } else {
       const size_t slot = ((size_t)r * nq + h) * num_splits + split;
@@ -501,13 +503,16 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     const float mb = s1 < eff_splits ? __ldcg(&part_ml[(base + s1) * 2]) : -CUDART_INF_F;
     const float la = s0 < eff_splits ? __ldcg(&part_ml[(base + s0) * 2 + 1]) : 0.f;
     const float lb = s1 < eff_splits ? __ldcg(&part_ml[(base + s1) * 2 + 1]) : 0.f;
-    const float mm = warp_max(fmaxf(ma, mb));
+    float mm = warp_max(fmaxf(ma, mb));
+    const bool sunk = ex.sink != nullptr && mm != -CUDART_INF_F;
+    if (sunk) mm = fmaxf(mm, ex.sink[h0 + hh]);
     const float fa = (mm == -CUDART_INF_F || s0 >= eff_splits) ? 0.f : __expf(ma - mm);
     const float fb = (mm == -CUDART_INF_F || s1 >= eff_splits) ? 0.f : __expf(mb - mm);
     if (s0 < eff_splits) f_s[hh * 64 + s0] = fa;
     if (s1 < eff_splits) f_s[hh * 64 + s1] = fb;
-    const float ll = warp_sum(la * fa + lb * fb);  // a butterfly: the same order whichever block merges
-    if (lane == 0) inv_s[hh] = ll > 0.f ? 1.f / ll : 0.f;
+    float ll = warp_sum(la * fa + lb * fb);  // a butterfly: the same order whichever block merges
+    if (sunk) ll += __expf(ex.sink[h0 + hh] - mm);
+    if (lane == 0) inv_s[hh] = ll > 0.f ? attn_gate<__nv_bfloat16>(ex, t, h0 + hh) / ll : 0.f;
   }
   __syncthreads();
   for (int idx = tid; idx < n_heads * (HD / 4); idx += kThreads) {
@@ -531,11 +536,12 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
 
 __global__ void attention_merge_bf16_kernel2(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_acc,
                                             const float* __restrict__ part_ml, int row0, int nq, int hd,
-                                            int num_splits) {
+                                            int num_splits, AttnExtra ex) {
   ccb::pdl_begin();
   const int r = blockIdx.x, h = blockIdx.y;
   const size_t base = ((size_t)r * nq + h) * num_splits;
   __nv_bfloat16* o = out + ((size_t)(row0 + r) * nq + h) * hd;
+  const float gt = attn_gate<__nv_bfloat16>(ex, row0 + r, h);
   // Eight splits at a time: their maxima, sums and outputs are all asked for before any is used, and are
   // folded in ascending order into a running (maximum, sum, output), as the attention kernels do with keys.
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
@@ -564,6 +570,7 @@ __global__ void attention_merge_bf16_kernel2(__nv_bfloat16* __restrict__ out, co
       }
       mm = mx;
     }
+    a *= attn_sink_fold(ex, h, mm, ll) * gt;
     o[d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
   }
 }
@@ -573,7 +580,7 @@ int launch(const void* q, const FusedQkv& fq, const void* k_cache, const void* v
            float* part_ml,
            const int* positions, const int* entry_of_token, const int* block_table, int bt_stride, int n_entries,
            int row0, int n_rows, int nq, int nkv, int page_size, int num_pages, int window, float scale,
-           int num_splits, int* counters, int* status, cudaStream_t stream) {
+           int num_splits, int* counters, AttnExtra ex, int* status, cudaStream_t stream) {
   const int G = nq / nkv, gchunks = (G + 15) / 16;
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
@@ -593,17 +600,18 @@ int launch(const void* q, const FusedQkv& fq, const void* k_cache, const void* v
   dim3 grid(n_rows, nkv * gchunks, num_splits);
   ccb_launch_ex(FUSED && fq.k_cache != nullptr, attention_decode_tma_kernel<HD, FUSED>, grid, kThreads, smem, stream,
                 tmK, tmV, (const __nv_bfloat16*)q, fq, (__nv_bfloat16*)out, part_acc, part_ml, positions, entry_of_token, block_table, bt_stride, n_entries,
-             row0, nq, nkv, page_size, page_shift, num_pages, window, scale, num_splits, counters, status);
+             row0, nq, nkv, page_size, page_shift, num_pages, window, scale, num_splits, counters, ex, status);
   int rc = ccb_launch_status();
   if (rc != 0 || num_splits == 1 || counters != nullptr) return rc;
   ccb_launch(attention_merge_bf16_kernel2, dim3(n_rows, nq), 128, 0, stream, (__nv_bfloat16*)out, part_acc, part_ml,
-             row0, nq, HD, num_splits);
+             row0, nq, HD, num_splits, ex);
   return ccb_launch_status();
 }
 
 }  // namespace
 
 // As ccb_attention_decode_mma, for page sizes that are a power of two from 8 to 64 (others: CCB_REFUSE_SIZE).
+// chunk, sink, gate, gate_stride: see AttnExtra (0 / null: none).
 // `counters` (optional): n_rows * kv_heads * ceil(group / 16) ints that are zero before the first launch and
 // are left zero; with them the splits are merged by the attention kernel itself, without them by a second
 // kernel.
@@ -612,8 +620,11 @@ CCB_API int ccb_attention_decode_tma(const void* q, const void* k_cache, const v
                                      const int* entry_of_token, const int* block_table, int bt_stride,
                                      int n_entries, int row0, int n_rows, int nq, int nkv, int hd, int page_size,
                                      int num_pages, int window, float scale, int num_splits, int* counters,
+                                     int chunk, const float* sink, const void* gate, int gate_stride,
                                      int* status, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (chunk < 0 || (gate != nullptr && gate_stride < nq)) return CCB_REFUSE_ARG;
+  const AttnExtra ex{chunk, sink, gate, gate_stride};
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || bt_stride <= 0 || num_splits <= 0 || num_splits > 64 ||
       page_size < 8 || page_size > 64 || (page_size & (page_size - 1)) != 0 ||
       ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) != 0)
@@ -623,11 +634,11 @@ CCB_API int ccb_attention_decode_tma(const void* q, const void* k_cache, const v
   if (hd == 128)
     return launch<128, false>(q, none, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
                               block_table, bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window,
-                              scale, num_splits, counters, status, stream);
+                              scale, num_splits, counters, ex, status, stream);
   if (hd == 64)
     return launch<64, false>(q, none, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
                              block_table, bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window,
-                             scale, num_splits, counters, status, stream);
+                             scale, num_splits, counters, ex, status, stream);
   return CCB_REFUSE_SIZE;
 }
 
@@ -646,8 +657,11 @@ CCB_API int ccb_attention_decode_tma_fused(const void* qkv, int qkv_stride, void
                                            int page_size, int num_pages, int window, float scale, int num_splits,
                                            const float* q_w, const float* k_w, float eps, const float* inv_freq,
                                            int write_kv, const float* bias, float qt_coef, int qt_every,
-                                           int* counters, int* status, cudaStream_t stream) {
+                                           int* counters, int chunk, const float* sink, const void* gate,
+                                           int gate_stride, int* status, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (chunk < 0 || (gate != nullptr && gate_stride < nq)) return CCB_REFUSE_ARG;
+  const AttnExtra ex{chunk, sink, gate, gate_stride};
   if (qt_every < 0 || (bias != nullptr && !write_kv)) return CCB_REFUSE_ARG;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || bt_stride <= 0 || num_splits <= 0 || num_splits > 64 ||
       page_size < 8 || page_size > 64 || (page_size & (page_size - 1)) != 0 || (qkv_stride & 1) ||
@@ -671,10 +685,10 @@ CCB_API int ccb_attention_decode_tma_fused(const void* qkv, int qkv_stride, void
   if (hd == 128)
     return launch<128, true>(nullptr, fq, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
                              block_table, bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window,
-                             scale, num_splits, counters, status, stream);
+                             scale, num_splits, counters, ex, status, stream);
   if (hd == 64)
     return launch<64, true>(nullptr, fq, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
                             block_table, bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window,
-                            scale, num_splits, counters, status, stream);
+                            scale, num_splits, counters, ex, status, stream);
   return CCB_REFUSE_SIZE;
 }

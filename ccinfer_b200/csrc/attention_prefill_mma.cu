@@ -31,7 +31,8 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
                              const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
                              const int* __restrict__ cu_q, const int* __restrict__ pos0,
                              const int* __restrict__ block_table, int bt_stride, int entry0, int nq, int nkv,
-                             int page_size, int num_pages, int window, float scale_log2, int* status) {
+                             int page_size, int num_pages, int window, float scale_log2, AttnExtra ex,
+                             int* status) {
   ccb::pdl_begin();
   constexpr int CH = HD / 8;
   constexpr int KS = HD / 16;
@@ -70,7 +71,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   }
   cp_async_commit();
 
-  const int j_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;  // first key any row sees
+  const int j_lo = first_visible_key(p_first, window, ex.chunk);  // first key any row sees
   const int first_tile = j_lo / kKTile, last_tile = p_last / kKTile;
   const int n_tiles = last_tile - first_tile + 1;
 
@@ -123,7 +124,9 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   cp_async_commit();
   // rows gid and gid + 8 of the warp: their positions and the first key each may see
   const int pr0 = p_first + warp * 16 + gid, pr1 = pr0 + 8;
-  const int lo0 = window > 0 ? max(0, pr0 - window + 1) : 0, lo1 = window > 0 ? max(0, pr1 - window + 1) : 0;
+  const int lo0 = first_visible_key(pr0, window, ex.chunk), lo1 = first_visible_key(pr1, window, ex.chunk);
+  // (a chunked mask: the rows of a warp whose runs all start behind a tile's last key skip the tile)
+  const int warp_lo = first_visible_key(p_first + warp * 16, window, ex.chunk);
 
   float o[2 * KS][4];
 #pragma unroll
@@ -139,7 +142,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     const __nv_bfloat16* vs_ = v_s + (it % kPStages) * TILE_ELEMS;
     const int jt = (first_tile + it) * kKTile;
     // a warp whose rows all lie before this tile's first key has nothing to do in it (causal)
-    const bool warp_active = jt <= p_first + warp * 16 + 15;
+    const bool warp_active = jt <= p_first + warp * 16 + 15 && jt + kKTile > warp_lo;
     if (warp_active) {
       float s[8][4];
 #pragma unroll
@@ -223,7 +226,23 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
   const int r0 = warp * 16 + gid, r1 = r0 + 8;
-  const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+  if (ex.sink != nullptr) {   // one more term in each denominator (m is in the base-2 scale of the scores)
+    const float sk = ex.sink[h] * 1.4426950408889634f;
+    const float n0 = fmaxf(m0, sk), n1 = fmaxf(m1, sk);
+    const float f0 = m0 == -CUDART_INF_F ? 0.f : exp2f(m0 - n0), f1 = m1 == -CUDART_INF_F ? 0.f : exp2f(m1 - n1);
+    l0 = l0 * f0 + exp2f(sk - n0);
+    l1 = l1 * f1 + exp2f(sk - n1);
+#pragma unroll
+    for (int i = 0; i < 2 * KS; ++i) {
+      o[i][0] *= f0; o[i][1] *= f0;
+      o[i][2] *= f1; o[i][3] *= f1;
+    }
+  }
+  float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+  if (ex.gate != nullptr) {
+    if (r0 < rows_here) inv0 *= attn_gate<__nv_bfloat16>(ex, row_begin + q_first + r0, h);
+    if (r1 < rows_here) inv1 *= attn_gate<__nv_bfloat16>(ex, row_begin + q_first + r1, h);
+  }
   __nv_bfloat16* o0 = out + ((size_t)(row_begin + q_first + r0) * nq + h) * HD;
   __nv_bfloat16* o1 = out + ((size_t)(row_begin + q_first + r1) * nq + h) * HD;
 #pragma unroll
@@ -237,7 +256,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
 template <int HD>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cu_q, const int* pos0,
            const int* block_table, int bt_stride, int entry0, int n_entries, int max_new, int nq, int nkv,
-           int page_size, int num_pages, int window, float scale, int* status, cudaStream_t stream) {
+           int page_size, int num_pages, int window, float scale, AttnExtra ex, int* status, cudaStream_t stream) {
   const size_t smem = (size_t)(2 * kPStages * kKTile * HD) * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
@@ -250,7 +269,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, c
   ccb_launch(attention_prefill_mma_kernel<HD>, grid, kPThreads, smem, stream, 
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
       cu_q, pos0, block_table, bt_stride, entry0, nq, nkv, page_size, num_pages, window,
-      scale * 1.4426950408889634f, status);
+      scale * 1.4426950408889634f, ex, status);
   return ccb_launch_status();
 }
 
@@ -258,20 +277,25 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, c
 
 // Requests entry0 .. entry0 + n_entries - 1 of the step (cu_q, pos0 and block_table rows are indexed by the
 // request's place in the step); max_new = the most new tokens any of them brings.  bfloat16, head size 64
-// or 128; other sizes are refused and belong to ccb_attention_split.
+// or 128; other sizes are refused and belong to ccb_attention_split.  chunk, sink, gate, gate_stride: see AttnExtra
+// (0 / null: none).
 CCB_API int ccb_attention_prefill_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
                                       const int* cu_q, const int* pos0, const int* block_table, int bt_stride,
                                       int entry0, int n_entries, int max_new, int nq, int nkv, int hd,
-                                      int page_size, int num_pages, int window, float scale, int* status,
+                                      int page_size, int num_pages, int window, float scale, int chunk,
+                                      const float* sink, const void* gate, int gate_stride, int* status,
                                       cudaStream_t stream) {
   if (n_entries <= 0 || max_new <= 0) return 0;
-  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || bt_stride <= 0 || n_entries > 65535 || nq > 65535)
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || bt_stride <= 0 || n_entries > 65535 || nq > 65535 ||
+      chunk < 0)
     return CCB_REFUSE_SIZE;
+  if (gate != nullptr && gate_stride < nq) return CCB_REFUSE_ARG;
+  const AttnExtra ex{chunk, sink, gate, gate_stride};
   if (hd == 128)
     return launch<128>(q, k_cache, v_cache, out, cu_q, pos0, block_table, bt_stride, entry0, n_entries, max_new,
-                       nq, nkv, page_size, num_pages, window, scale, status, stream);
+                       nq, nkv, page_size, num_pages, window, scale, ex, status, stream);
   if (hd == 64)
     return launch<64>(q, k_cache, v_cache, out, cu_q, pos0, block_table, bt_stride, entry0, n_entries, max_new, nq,
-                      nkv, page_size, num_pages, window, scale, status, stream);
+                      nkv, page_size, num_pages, window, scale, ex, status, stream);
   return CCB_REFUSE_SIZE;
 }

@@ -86,7 +86,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                             const int* __restrict__ cu_q, const int* __restrict__ pos0,
                             const int* __restrict__ block_table, int bt_stride, int entry0, int nq, int nkv,
                             int page_size, int page_shift, int num_pages, int window, float scale_log2,
-                            int* status) {
+                            AttnExtra ex, int* status) {
   constexpr int HD = 64 * NH;
   constexpr int HALF_BYTES = 128 * 128;            // 128 rows x 128 bytes: one 64-column half of a tile
   constexpr int TILE_BYTES = NH * HALF_BYTES;      // Q, K or V tile
@@ -118,7 +118,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
   const int rows_here = min(kTQ, n_new - q_first);
   const int p_first = p0 + q_first, p_last = p_first + rows_here - 1;
   const int* bt = block_table + (size_t)b * bt_stride;
-  const int j_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  const int j_lo = first_visible_key(p_first, window, ex.chunk);   // the first key any row of the tile sees
   const int first_tile = j_lo / kTK, last_tile = p_last / kTK;
   const int n_tiles = last_tile - first_tile + 1;
 
@@ -257,7 +257,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     const int row = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const int pr = p_first + row;                                   // this row's position
-    const int lo = window > 0 ? max(0, pr - window + 1) : 0;        // first key it may see
+    const int lo = first_visible_key(pr, window, ex.chunk);         // first key it may see
+    const int lo_last = first_visible_key(p_first + kTQ - 1, window, ex.chunk);   // the tile's last row's
     float m = -CUDART_INF_F, l = 0.f;
     bool alive = true;
     for (int i = 0; i < n_tiles; ++i) {
@@ -267,7 +268,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
       const int jt = (first_tile + i) * kTK;
       const uint32_t tmem_si = tmem_s + (i & 1) * 128;
       // Most tiles lie wholly in every row's past (and inside its window): they need no mask.
-      const bool need_mask = (jt + kTK - 1 > p_first) || (window > 0 && jt < p_first + kTQ - window);
+      const bool need_mask = (jt + kTK - 1 > p_first) || jt < lo_last;
       // the row's 128 scores, read once
       uint32_t v[kTK];
 #pragma unroll
@@ -346,7 +347,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     if (!alive && lane == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
     pdl_trigger();
     if (alive) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float inv = l > 0.f ? 1.f / l : 0.f;
+      if (ex.sink != nullptr && m != -CUDART_INF_F) {
+        // one more term in the denominator; m and l are in the base-2 scale of the scores
+        const float sk = ex.sink[h] * 1.4426950408889634f;
+        const float m2 = fmaxf(m, sk);
+        const float f = ex2(m - m2);
+        inv = f / (l * f + ex2(sk - m2));
+      }
+      if (row < rows_here) inv *= attn_gate<__nv_bfloat16>(ex, row_begin + q_first + row, h);
       __nv_bfloat16* orow = out + ((size_t)(row_begin + q_first + row) * nq + h) * HD;
 #pragma unroll 1
       for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -402,7 +411,7 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const 
                                  const int* __restrict__ cu_q, const int* __restrict__ pos0,
                                  const int* __restrict__ block_table, int bt_stride, int entry0, int nq, int nkv,
                                  int page_size, int page_shift, int num_pages, int window, float scale_log2,
-                                 int* status) {
+                                 AttnExtra ex, int* status) {
   constexpr int HD = 64 * NH;
   constexpr int HALF_BYTES = 128 * 128;
   constexpr int TILE_BYTES = NH * HALF_BYTES;
@@ -432,7 +441,7 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const 
   const int rows_here = min(kTQ, n_new - q_first);
   const int p_first = p0 + q_first, p_last = p_first + rows_here - 1;
   const int* bt = block_table + (size_t)b * bt_stride;
-  const int j_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  const int j_lo = first_visible_key(p_first, window, ex.chunk);   // the first key any row of the tile sees
   const int first_tile = j_lo / kTK, last_tile = p_last / kTK;
   const int n_tiles = last_tile - first_tile + 1;
 
@@ -574,7 +583,8 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const 
     const uint32_t tmem_sx = tmem_base + x * 128, tmem_ox = tmem_base + 256 + x * 128;
     const uint32_t bar_sf = b_sf + 8 * x, bar_pr = b_pr + 8 * x, bar_pv = b_pv + 8 * x;
     const int pr = p_first + row;
-    const int lo = window > 0 ? max(0, pr - window + 1) : 0;
+    const int lo = first_visible_key(pr, window, ex.chunk);         // first key it may see
+    const int lo_last = first_visible_key(p_first + kTQ - 1, window, ex.chunk);   // the tile's last row's
     float m = -CUDART_INF_F, l = 0.f;
     bool alive = true;
     for (int i = 0; i < n_tiles; ++i) {
@@ -582,7 +592,7 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const 
       if (!alive) break;
       tc_fence_after();
       const int jt = (first_tile + i) * kTK;
-      const bool need_mask = (jt + kTK - 1 > p_first) || (window > 0 && jt < p_first + kTQ - window);
+      const bool need_mask = (jt + kTK - 1 > p_first) || jt < lo_last;
       uint32_t v[kTK];
 #pragma unroll
       for (int c0 = 0; c0 < kTK; c0 += 32) tc_ld32(tmem_sx + lane_addr + c0, v + c0);
@@ -654,7 +664,15 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const 
     if (!alive && lane == 0) set_status(status, CCB_ST_WAIT_TIMEOUT);
     pdl_trigger();
     if (alive) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float inv = l > 0.f ? 1.f / l : 0.f;
+      if (ex.sink != nullptr && m != -CUDART_INF_F) {
+        // one more term in the denominator; m and l are in the base-2 scale of the scores
+        const float sk = ex.sink[h] * 1.4426950408889634f;
+        const float m2 = fmaxf(m, sk);
+        const float f = ex2(m - m2);
+        inv = f / (l * f + ex2(sk - m2));
+      }
+      if (row < rows_here) inv *= attn_gate<__nv_bfloat16>(ex, row_begin + q_first + row, h);
       __nv_bfloat16* orow = out + ((size_t)(row_begin + q_first + row) * nq + h) * HD;
 #pragma unroll 1
       for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -689,7 +707,8 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const 
 template <int NH>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cu_q, const int* pos0,
            const int* block_table, int bt_stride, int entry0, int n_entries, int max_new, int n_tokens, int nq,
-           int nkv, int page_size, int num_pages, int window, float scale, int* status, cudaStream_t stream) {
+           int nkv, int page_size, int num_pages, int window, float scale, AttnExtra ex, int* status,
+           cudaStream_t stream) {
   constexpr int HD = 64 * NH;
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
@@ -714,7 +733,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, c
     dim3 grid2(nq / 2, (max_new + kTQ - 1) / kTQ, n_entries);
     ccb_launch(attention_prefill_tc_pair_kernel<NH>, grid2, kPairThreads, smem2, stream, tmQ, tmK, tmV,
                (__nv_bfloat16*)out, cu_q, pos0, block_table, bt_stride, entry0, nq, nkv, page_size, page_shift,
-               num_pages, window, scale * 1.4426950408889634f, status);
+               num_pages, window, scale * 1.4426950408889634f, ex, status);
     return ccb_launch_status();
   }
   const size_t smem = (size_t)(1 + 2 * kKvStages) * NH * 128 * 128 + 20 * 8 + 1024;
@@ -728,20 +747,24 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, c
   dim3 grid(nq, (max_new + kTQ - 1) / kTQ, n_entries);
   ccb_launch(attention_prefill_tc_kernel<NH>, grid, kTcThreads, smem, stream, tmQ, tmK, tmV, (__nv_bfloat16*)out, cu_q,
              pos0, block_table, bt_stride, entry0, nq, nkv, page_size, page_shift, num_pages, window,
-             scale * 1.4426950408889634f, status);
+             scale * 1.4426950408889634f, ex, status);
   return ccb_launch_status();
 }
 
 }  // namespace
 
 // As ccb_attention_prefill_mma; n_tokens = rows of q / out.  bfloat16, head size 64 or 128, page size a power
-// of two from 8 to 128; anything else is refused (CCB_REFUSE_SIZE) and belongs to the other kernels.
+// of two from 8 to 128; anything else is refused (CCB_REFUSE_SIZE) and belongs to the other kernels.  chunk, sink,
+// gate, gate_stride: see AttnExtra (0 / null: none).
 CCB_API int ccb_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
                                      const int* cu_q, const int* pos0, const int* block_table, int bt_stride,
                                      int entry0, int n_entries, int max_new, int n_tokens, int nq, int nkv, int hd,
-                                     int page_size, int num_pages, int window, float scale, int* status,
+                                     int page_size, int num_pages, int window, float scale, int chunk,
+                                     const float* sink, const void* gate, int gate_stride, int* status,
                                      cudaStream_t stream) {
   if (n_entries <= 0 || max_new <= 0) return 0;
+  if (chunk < 0 || (gate != nullptr && gate_stride < nq)) return CCB_REFUSE_ARG;
+  const AttnExtra ex{chunk, sink, gate, gate_stride};
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || bt_stride <= 0 || n_entries > 65535 || nq > 65535 || page_size < 8 ||
       page_size > 128 || (page_size & (page_size - 1)) != 0 ||
       ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
@@ -749,10 +772,10 @@ CCB_API int ccb_attention_prefill_tc(const void* q, const void* k_cache, const v
     return CCB_REFUSE_SIZE;
   if (hd == 128)
     return launch<2>(q, k_cache, v_cache, out, cu_q, pos0, block_table, bt_stride, entry0, n_entries, max_new,
-                     n_tokens, nq, nkv, page_size, num_pages, window, scale, status, stream);
+                     n_tokens, nq, nkv, page_size, num_pages, window, scale, ex, status, stream);
   if (hd == 64)
     return launch<1>(q, k_cache, v_cache, out, cu_q, pos0, block_table, bt_stride, entry0, n_entries, max_new,
-                     n_tokens, nq, nkv, page_size, num_pages, window, scale, status, stream);
+                     n_tokens, nq, nkv, page_size, num_pages, window, scale, ex, status, stream);
   return CCB_REFUSE_SIZE;
 }
 

@@ -138,6 +138,18 @@ __device__ __forceinline__ int first_visible_key(int p, int window, int chunk) {
   return j0;
 }
 
+// The sink's term folded into a finished softmax of head h (maximum mm, sum ll, natural exponent): ll becomes the
+// whole denominator, and the weighted values are to be multiplied by the factor returned.  A row that saw no key
+// (mm = -inf, a padded row) is left as it is.
+__device__ __forceinline__ float attn_sink_fold(const AttnExtra& ex, int h, float mm, float& ll) {
+  if (ex.sink == nullptr || mm == -INFINITY) return 1.f;
+  const float sk = ex.sink[h];
+  const float m2 = fmaxf(mm, sk);
+  const float f = __expf(mm - m2);
+  ll = ll * f + __expf(sk - m2);
+  return f;
+}
+
 template <typename T>
 __device__ __forceinline__ float attn_gate(const AttnExtra& ex, int t, int h) {
   if (ex.gate == nullptr) return 1.f;

@@ -392,7 +392,8 @@ __device__ __forceinline__ uint4 ld16_or_zero(const __nv_bfloat16* p, bool ok) {
   return ok ? *reinterpret_cast<const uint4*>(p) : make_uint4(0u, 0u, 0u, 0u);
 }
 
-// MODE 0: C (compute type) = relu(c)^2 * row_w[row];  MODE 1: C (float) = c.
+// MODE 0: C (compute type) = relu(c)^2 * row_w[row];  MODE 1: C (float) = c;  MODE 2: the matrix's rows are
+// gate and up rows in turn and C (compute type) [*, N / 2] = silu(gate) * up * row_w[row].
 // A [*, lda]: row src_row[r] (MODE 0) or r itself (src_row null).  W_e = W + e * w_expert_stride, rows at ldw.
 // Few rows an expert (tiles of 16, a decode step): the product is a stream of the chosen experts' matrices, and
 // what counts is bytes in flight.  A block takes 8 columns of a tile; its four warps take a quarter of k each
@@ -479,6 +480,9 @@ moe_grouped_rows16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const in
       __nv_bfloat16* c = (__nv_bfloat16*)Cout + g * ldc + c0;
       if (c0 < N) c[0] = __float2bfloat16_rn(v0);
       if (c0 + 1 < N) c[1] = __float2bfloat16_rn(v1);
+    } else if (MODE == 2) {   // columns (2 f, 2 f + 1) are gate f and up f: one number of the gated activation
+      if (c0 + 1 < N)
+        ((__nv_bfloat16*)Cout)[g * ldc + (c0 >> 1)] = __float2bfloat16_rn(v0 / (1.f + __expf(-v0)) * v1 * row_w[g]);
     } else {
       float* c = (float*)Cout + g * ldc + c0;
       if (c0 < N) c[0] = v0;
@@ -524,6 +528,15 @@ moe_grouped_f32_kernel(const float* __restrict__ A, int lda, const int* __restri
 #pragma unroll
       for (int r = 0; r < 16; ++r) acc[r] = fmaf(As[r][k], w, acc[r]);
     }
+  }
+  if (MODE == 2) {   // columns (2 f, 2 f + 1) are gate f and up f (N is even: a pair lies in one warp)
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      const float up = __shfl_down_sync(0xffffffffu, acc[r], 1);
+      if (r < n_rows && col + 1 < N && !(col & 1))
+        C[(size_t)(r0 + r) * ldc + (col >> 1)] = acc[r] / (1.f + expf(-acc[r])) * up * row_w[r0 + r];
+    }
+    return;
   }
   if (col >= N) return;
   for (int r = 0; r < n_rows; ++r) {
@@ -617,17 +630,21 @@ CCB_API int ccb_moe_route_sort(const float* logits, int ldl, const float* correc
 }
 
 // mode 0: C (the compute type) [sorted rows, N] = relu(A[src_row] W_e^T)^2 * row_w;  mode 1: C (float) = A W_e^T
-// with A's rows the sorted rows themselves.  Tiles of 16 rows (what moe_sort was given).
+// with A's rows the sorted rows themselves;  mode 2: W_e's N rows are gate and up rows in turn, C (the compute
+// type) [sorted rows, N / 2] = silu(gate) * up * row_w.  Tiles of 16 rows (what moe_sort was given).
 CCB_API int ccb_moe_grouped(const void* A, int lda, const int* src_row, const void* W, int ldw,
                             long long w_expert_stride, void* C, int ldc, const float* row_w, const int* tile_e,
                             const int* tile_r0, const int* tile_n, int max_tiles, int N, int K, int BM, int mode,
                             int dtype, cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0) return 0;
-  if (K <= 0 || (mode != 0 && mode != 1)) return CCB_REFUSE_SIZE;
+  if (K <= 0 || mode < 0 || mode > 2 || (mode == 2 && (N & 1))) return CCB_REFUSE_SIZE;
   if (dtype == CCB_F32) {
     if (BM != 16) return CCB_REFUSE_SIZE;
     dim3 grid(max_tiles, (N + 127) / 128);
-    if (mode == 0)
+    if (mode == 2)
+      ccb_launch(moe_grouped_f32_kernel<2>, grid, dim3(128), 0, stream, (const float*)A, lda, src_row, (const float*)W,
+                 ldw, w_expert_stride, (float*)C, ldc, row_w, tile_e, tile_r0, tile_n, N, K);
+    else if (mode == 0)
       ccb_launch(moe_grouped_f32_kernel<0>, grid, dim3(128), 0, stream, (const float*)A, lda, src_row, (const float*)W,
                  ldw, w_expert_stride, (float*)C, ldc, row_w, tile_e, tile_r0, tile_n, N, K);
     else
@@ -644,7 +661,10 @@ CCB_API int ccb_moe_grouped(const void* A, int lda, const int* src_row, const vo
   // for the whole part at 128 tokens, 32 experts of 1536 x 4096 of which 4 are chosen)
   if (BM != 16) return CCB_REFUSE_SIZE;
   dim3 grid16((N + 7) / 8, max_tiles);   // the tiles that hold rows come first in the list, and so do their blocks
-  if (mode == 0)
+  if (mode == 2)
+    ccb_launch(moe_grouped_rows16_kernel<2>, grid16, dim3(128), 0, stream, (const __nv_bfloat16*)A, lda, src_row,
+               (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, row_w, tile_e, tile_r0, tile_n, N, K);
+  else if (mode == 0)
     ccb_launch(moe_grouped_rows16_kernel<0>, grid16, dim3(128), 0, stream, (const __nv_bfloat16*)A, lda, src_row,
                (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, row_w, tile_e, tile_r0, tile_n, N, K);
   else

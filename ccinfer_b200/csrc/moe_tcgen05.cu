@@ -32,7 +32,9 @@ __host__ __device__ constexpr uint32_t instr_desc(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
-// MODE 0: B rows at e * F + tile column, C bfloat16 = relu(c)^2 * row_w;  MODE 1: B columns at e * F + k, C float.
+// MODE 0: B rows at e * F + tile column, C bfloat16 = relu(c)^2 * row_w;  MODE 1: B columns at e * F + k, C float;
+// MODE 2: as MODE 0 with B's rows gate and up rows in turn (F rows an expert, N = F), C bfloat16 [*, N / 2] =
+// silu(gate) * up * row_w.
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -55,8 +57,8 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tileB = blockIdx.y;
   const int nkb = (K + BK - 1) / BK;
-  const int b_row = MODE == 0 ? e * F + tileB * BN : tileB * BN;
-  const int b_col = MODE == 0 ? 0 : e * F;
+  const int b_row = MODE != 1 ? e * F + tileB * BN : tileB * BN;
+  const int b_col = MODE != 1 ? 0 : e * F;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -118,7 +120,7 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     if (ok) {
       const size_t g = (size_t)(r0 + row);
       const bool mine = row < n_rows;
-      const float wr = (MODE == 0 && mine) ? row_w[g] : 1.f;
+      const float wr = (MODE != 1 && mine) ? row_w[g] : 1.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         uint32_t v[16];
@@ -142,6 +144,23 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           } else {
             const __nv_bfloat16* ph = reinterpret_cast<const __nv_bfloat16*>(p);
             for (int i = 0; i < n_valid; ++i) dst[i] = ph[i];
+          }
+        } else if (MODE == 2) {   // columns (2 f, 2 f + 1) are gate f and up f
+          __nv_bfloat16* dst = (__nv_bfloat16*)Cout + g * ldc + (col >> 1);
+          uint32_t p[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float g0 = __uint_as_float(v[4 * i]), u0 = __uint_as_float(v[4 * i + 1]);
+            const float g1 = __uint_as_float(v[4 * i + 2]), u1 = __uint_as_float(v[4 * i + 3]);
+            const __nv_bfloat162 h = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0 * wr,
+                                                           g1 / (1.f + __expf(-g1)) * u1 * wr);
+            p[i] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+          if (n_valid == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            reinterpret_cast<uint4*>(dst)[0] = make_uint4(p[0], p[1], p[2], p[3]);
+          } else {
+            const __nv_bfloat16* ph = reinterpret_cast<const __nv_bfloat16*>(p);
+            for (int i = 0; i < n_valid / 2; ++i) dst[i] = ph[i];
           }
         } else {
           float* dst = (float*)Cout + g * ldc + col;
@@ -214,18 +233,21 @@ CCB_API int ccb_moe_gather_rows(void* out, const void* x, const int* src_row, in
 // The tiles are those of moe_sort with BM = 128.  A [rows, K] holds the sorted rows (contiguous rows of lda).
 // mode 0: W = the first matrices stacked [w_rows, K] (expert e at row e * F), C bfloat16 [rows, N = F] with
 // relu(.)^2 * row_w;  mode 1: W = the second matrices side by side [N, w_cols] (expert e at column e * F, K = F),
-// C float [rows, N].
+// C float [rows, N];  mode 2: W = the first matrices stacked with every expert's gate and up rows in turn (F rows an
+// expert, N = F), C bfloat16 [rows, N / 2] = silu(gate) * up * row_w.
 CCB_API int ccb_moe_grouped_tc(const void* A, int lda, int rows, const void* W, int ldw, int w_rows, int w_cols,
                                void* C, int ldc, const float* row_w, const int* tile_e, const int* tile_r0,
                                const int* tile_n, int max_tiles, int N, int K, int F, int mode, int* status,
                                cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0 || rows <= 0) return 0;
-  if (K <= 0 || (K & 7) || (F & 7) || (lda & 7) || (ldw & 7) || (mode != 0 && mode != 1) ||
+  if (K <= 0 || (K & 7) || (F & 7) || (lda & 7) || (ldw & 7) || mode < 0 || mode > 2 || (mode == 2 && (N & 1)) ||
       (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
     return CCB_REFUSE_SIZE;
   CUtensorMap tmA, tmB;
   if (!ccb_tensor_map_2d(A, rows, K, lda, BK, BM, &tmA) || !ccb_tensor_map_2d(W, w_rows, w_cols, ldw, BK, 256, &tmB))
     return CCB_REFUSE_ARG;
+  if (mode == 2)
+    return launch<2>(tmA, tmB, C, ldc, row_w, tile_e, tile_r0, tile_n, max_tiles, N, K, F, status, stream);
   if (mode == 0)
     return launch<0>(tmA, tmB, C, ldc, row_w, tile_e, tile_r0, tile_n, max_tiles, N, K, F, status, stream);
   return launch<1>(tmA, tmB, C, ldc, row_w, tile_e, tile_r0, tile_n, max_tiles, N, K, F, status, stream);

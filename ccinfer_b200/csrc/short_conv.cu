@@ -41,7 +41,7 @@ conv_rows_kernel(const T* __restrict__ in, int in_stride, T* __restrict__ out, i
     return;
   }
   const int r0 = cu_q[b], n = cu_q[b + 1] - r0, i = t - r0;
-  int slot = state_slot[b];
+  int slot = state != nullptr ? state_slot[b] : -1;   // (one tap, or no convolution: there is no state)
   if (slot >= max_slots) {
     set_status(status, CCB_ST_BAD_SLOT);
     slot = -1;

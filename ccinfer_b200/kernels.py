@@ -128,22 +128,24 @@ _SIGNATURES = {
     "ccb_attention_split": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                             c_int, c_void_p, c_void_p],
+    # (the four arguments before the status word: chunk, sink, gate, gate_stride)
     "ccb_attention_decode_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                 c_float, c_int, c_void_p, c_void_p],
+                                 c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "ccb_attention_decode_tma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                 c_float, c_int, c_void_p, c_void_p, c_void_p],
+                                 c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "ccb_attention_decode_tma_fused": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int,
-                                       c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p],
-    "ccb_attention_prefill_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                  c_void_p],
+                                       c_void_p, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                       c_void_p, c_void_p],
+    "ccb_attention_prefill_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                     c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "ccb_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                 c_void_p],
+                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                 c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "ccb_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_cublas_create": [ctypes.POINTER(c_void_p)],
     "ccb_cublas_destroy": [c_void_p],
@@ -733,10 +735,12 @@ def moe_grouped(c, a, src_row, w, w_expert_stride: int, row_w, tile_e, tile_r0, 
                 mode: int) -> None:
     """The product of every tile's rows with its expert's matrix (``w`` [*, ldw] viewed from the first expert's
     first element, expert e at + e * w_expert_stride elements, N rows of K).  mode 0: c[row] = relu(a[src_row[row]]
-    W_e^T)^2 * row_w[row] in the compute type; mode 1: c[row] = a[row] W_e^T in float."""
+    W_e^T)^2 * row_w[row] in the compute type; mode 1: c[row] = a[row] W_e^T in float; mode 2: W_e's rows are gate
+    and up rows in turn (N of them), c[row] [N / 2] = silu(gate) * up * row_w[row] in the compute type."""
     _cuda(src_row, row_w, tile_e, tile_r0, tile_n)
     assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1 and a.dtype == w.dtype
-    assert c.dtype == (a.dtype if mode == 0 else torch.float32) and c.shape[1] == N and a.shape[1] == K
+    assert c.dtype == (torch.float32 if mode == 1 else a.dtype) and a.shape[1] == K
+    assert c.shape[1] == (N // 2 if mode == 2 else N)
     _check(lib().ccb_moe_grouped(_p(a), a.stride(0), _p(src_row), _p(w), w.stride(0), int(w_expert_stride), _p(c),
                                  c.stride(0), _p(row_w), _p(tile_e), _p(tile_r0), _p(tile_n), tile_e.numel(), N, K, BM,
                                  mode, _dt(a), _stream()), "moe_grouped")
@@ -758,10 +762,12 @@ def moe_gather_rows(out, x, src_row) -> None:
 def moe_grouped_tc(c, a, w, row_w, tile_e, tile_r0, tile_n, N: int, K: int, F: int, mode: int, status=None) -> None:
     """``moe_grouped`` on tcgen05 tensor cores for tiles of MOE_TC_ROWS sorted rows (bfloat16).  ``a`` holds the
     sorted rows themselves.  mode 0: ``w`` = all first matrices stacked [E F, K], c bfloat16 [rows, F] =
-    relu(a W_e^T)^2 * row_w;  mode 1: ``w`` = all second matrices side by side [N, E F] (K = F), c float."""
+    relu(a W_e^T)^2 * row_w;  mode 1: ``w`` = all second matrices side by side [N, E F] (K = F), c float;  mode 2:
+    as mode 0 with every expert's F = N rows gate and up rows in turn, c bfloat16 [rows, N / 2] = silu(gate) * up *
+    row_w."""
     _cuda(a, w, row_w, tile_e, tile_r0, tile_n, status)
-    assert a.dtype == w.dtype == torch.bfloat16 and c.dtype == (torch.bfloat16 if mode == 0 else torch.float32)
-    assert a.shape[1] == K and c.shape == (a.shape[0], N) and c.is_contiguous()
+    assert a.dtype == w.dtype == torch.bfloat16 and c.dtype == (torch.float32 if mode == 1 else torch.bfloat16)
+    assert a.shape[1] == K and c.shape == (a.shape[0], N // 2 if mode == 2 else N) and c.is_contiguous()
     _check(lib().ccb_moe_grouped_tc(_p(a), a.stride(0), a.shape[0], _p(w), w.stride(0), w.shape[0], w.shape[1], _p(c),
                                     c.stride(0), _p(row_w), _p(tile_e), _p(tile_r0), _p(tile_n), tile_e.numel(), N, K,
                                     F, mode, _p(status), _stream()), "moe_grouped_tc")
@@ -918,9 +924,18 @@ DECODE_MMA_HEAD_SIZES = (64, 128)
 DECODE_MMA_HEADS_PER_BLOCK = 16
 
 
+def _attn_extra(q_rows: int, nq: int, dtype, chunk: int, sink, gate):
+    """The four arguments ``chunk, sink, gate, gate_stride`` of the attention kernels (see ``attention_split``)."""
+    _cuda(sink)   # (the gate's rows are a view into a wider row)
+    assert chunk >= 0 and (sink is None or (sink.dtype == torch.float32 and sink.numel() == nq))
+    assert gate is None or (gate.is_cuda and gate.dtype == dtype and gate.stride(1) == 1 and gate.shape[0] == q_rows
+                            and gate.shape[1] >= nq)
+    return int(chunk), _p(sink), _p(gate), gate.stride(0) if gate is not None else 0
+
+
 def attention_decode_mma(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
                          n_entries: int, row0: int, n_rows: int, window: int, scale: float, num_splits: int,
-                         status=None) -> None:
+                         status=None, chunk: int = 0, sink=None, gate=None) -> None:
     """As attention_split, on tensor cores: bfloat16, head size 64 or 128, a block per (row, kv head, split)
     serving the whole group of q heads."""
     _cuda(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table, status)
@@ -935,7 +950,8 @@ def attention_decode_mma(q, k_cache, v_cache, out, part_acc, part_ml, positions,
     _check(lib().ccb_attention_decode_mma(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_acc), _p(part_ml),
                                           _p(positions), _p(entry_of_token), _p(block_table),
                                           block_table.stride(0), n_entries, row0, n_rows, nq, nkv, hd, page_size,
-                                          num_pages, int(window), float(scale), num_splits, _p(status),
+                                          num_pages, int(window), float(scale), num_splits,
+                                          *_attn_extra(T, nq, q.dtype, chunk, sink, gate), _p(status),
                                           _stream()), "attention_decode_mma")
     if num_splits > 1:
         counters.own += 1  # the merge kernel
@@ -947,7 +963,7 @@ def attention_decode_tma_fits(hd: int, page_size: int) -> bool:
 
 def attention_decode_tma(q, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table,
                          n_entries: int, row0: int, n_rows: int, window: int, scale: float, num_splits: int,
-                         status=None, merge_counters=None) -> None:
+                         status=None, merge_counters=None, chunk: int = 0, sink=None, gate=None) -> None:
     """As attention_decode_mma, with keys and values loaded page by page through TMA boxes by a producer warp
     (page size a power of two from 8 to 64).
 
@@ -972,16 +988,19 @@ def attention_decode_tma(q, k_cache, v_cache, out, part_acc, part_ml, positions,
                                           _p(positions), _p(entry_of_token), _p(block_table),
                                           block_table.stride(0), n_entries, row0, n_rows, nq, nkv, hd, page_size,
                                           num_pages, int(window), float(scale), num_splits, _p(merge_counters),
-                                          _p(status), _stream()), "attention_decode_tma")
+                                          *_attn_extra(T, nq, q.dtype, chunk, sink, gate), _p(status), _stream()),
+           "attention_decode_tma")
     if num_splits > 1 and merge_counters is None:
         counters.own += 1  # the merge kernel
 
 
 def attention_prefill_mma(q, k_cache, v_cache, out, cu_q, pos0, block_table, entry0: int, n_entries: int,
-                          max_new: int, window: int, scale: float, status=None) -> None:
+                          max_new: int, window: int, scale: float, status=None, chunk: int = 0, sink=None,
+                          gate=None) -> None:
     """Causal attention of the new tokens of the step's requests entry0 .. entry0 + n_entries - 1 over their
     pages, on tensor cores (bfloat16, head size 64 or 128).  cu_q [B + 1] gives each request's first token
-    row, pos0 [B] the position of that token; max_new is the most new tokens any of them has."""
+    row, pos0 [B] the position of that token; max_new is the most new tokens any of them has.  ``chunk``,
+    ``sink``, ``gate``: as for ``attention_split``."""
     _cuda(q, k_cache, v_cache, out, cu_q, pos0, block_table, status)
     T, nq, hd = q.shape
     num_pages, nkv, page_size, hd2 = k_cache.shape
@@ -989,21 +1008,22 @@ def attention_prefill_mma(q, k_cache, v_cache, out, cu_q, pos0, block_table, ent
     assert q.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16
     assert entry0 >= 0 and entry0 + n_entries <= block_table.shape[0] and cu_q.numel() >= entry0 + n_entries + 1
     _check(lib().ccb_attention_prefill_mma(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(cu_q), _p(pos0),
-                                           _p(block_table), block_table.stride(0), entry0, n_entries, max_new,
-                                           nq, nkv, hd, page_size, num_pages, int(window), float(scale),
-                                           _p(status), _stream()), "attention_prefill_mma")
+                                              _p(block_table), block_table.stride(0), entry0, n_entries, max_new,
+                                              nq, nkv, hd, page_size, num_pages, int(window), float(scale),
+                                              *_attn_extra(T, nq, q.dtype, chunk, sink, gate), _p(status),
+                                              _stream()), "attention_prefill_mma")
 
 
 def attention_decode_tma_fused(qkv, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
                                block_table, n_entries: int, row0: int, n_rows: int, nq: int, window: int,
                                scale: float, num_splits: int, q_norm_w, k_norm_w, eps: float, inv_freq,
                                write_kv: bool = True, status=None, merge_counters=None, bias=None,
-                               q_temperature=None) -> None:
+                               q_temperature=None, chunk: int = 0, sink=None, gate=None) -> None:
     """attention_decode_tma for rows of ONE new token each, straight from the q|k|v product ``qkv``
     [T, (nq + 2 nkv) * hd] (only the nq query heads when ``write_kv`` is false): the kernel norms and rotates
     the queries itself and, with ``write_kv``, also the row's key, which it writes with the value to their
     page and attends to.  qk_norm_rope_kv_write is not needed for these rows.  ``bias`` and ``q_temperature``
-    as for ``qkv_bias_rope_kv_write``."""
+    as for ``qkv_bias_rope_kv_write``; ``chunk``, ``sink``, ``gate`` as for ``attention_split``."""
     _cuda(qkv, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table, status,
           merge_counters, q_norm_w, k_norm_w, inv_freq, bias)
     assert bias is None or (write_kv and bias.dtype == torch.float32
@@ -1027,8 +1047,8 @@ def attention_decode_tma_fused(qkv, k_cache, v_cache, out, part_acc, part_ml, po
         _p(entry_of_token), _p(block_table), block_table.stride(0), n_entries, row0, n_rows, nq, nkv, hd, page_size,
         num_pages, int(window), float(scale), num_splits, _p(q_norm_w), _p(k_norm_w), float(eps), _p(inv_freq),
         1 if write_kv else 0, _p(bias), float(q_temperature[0]) if q_temperature else 0.0,
-        int(q_temperature[1]) if q_temperature else 0, _p(merge_counters), _p(status), _stream()),
-        "attention_decode_tma_fused")
+        int(q_temperature[1]) if q_temperature else 0, _p(merge_counters),
+        *_attn_extra(T, nq, qkv.dtype, chunk, sink, gate), _p(status), _stream()), "attention_decode_tma_fused")
     if num_splits > 1 and merge_counters is None:
         counters.own += 1  # the merge kernel
 
@@ -1038,7 +1058,8 @@ def attention_prefill_tc_fits(hd: int, page_size: int) -> bool:
 
 
 def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, pos0, block_table, entry0: int, n_entries: int,
-                         max_new: int, window: int, scale: float, status=None) -> None:
+                         max_new: int, window: int, scale: float, status=None, chunk: int = 0, sink=None,
+                         gate=None) -> None:
     """As attention_prefill_mma, with both products on tcgen05 tensor cores and the accumulators in tensor
     memory (128-token query tiles, TMA loads page by page).  Page size a power of two from 8 to 128.  Where the
     groups hold an even number of q heads, two heads of a group share a block and its key and value tiles."""
@@ -1051,7 +1072,8 @@ def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, pos0, block_table, entr
     _check(lib().ccb_attention_prefill_tc(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(cu_q), _p(pos0),
                                           _p(block_table), block_table.stride(0), entry0, n_entries, max_new, T,
                                           nq, nkv, hd, page_size, num_pages, int(window), float(scale),
-                                          _p(status), _stream()), "attention_prefill_tc")
+                                          *_attn_extra(T, nq, q.dtype, chunk, sink, gate), _p(status), _stream()),
+           "attention_prefill_tc")
 
 
 def attention_prefill_tc_single_head(on: bool) -> None:

@@ -91,7 +91,7 @@ class GroupedQueryAttention(Mixer):
             raise Unsupported("a layer that reads another layer's keys has no convolution, value mixing or gate")
         if (self.taps or self.value_mix) and self.has_bias:
             raise Unsupported("biases together with a convolution or value mixing")
-        # attention beyond keys and values: the kernels that take it are chosen in _attend
+        # attention beyond keys and values (every attention kernel takes them)
         self.extras = bool(self.chunk or "sink" in self.names or "gate" in self.names)
         self.float_weights = bool(float_weights)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.qk_dim)
@@ -229,8 +229,8 @@ class GroupedQueryAttention(Mixer):
         a prefill kernel (tcgen05 with 128 query tokens a block, or mma.sync with 64); otherwise every row is
         a single query of the split kernel, which takes all sizes and both types."""
         rt, g = self.rt, cache.group
-        mma = (rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES
-               and not self.float_weights and not self.extras)
+        mma = rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES and not self.float_weights
+        extra = {"chunk": self.chunk, "sink": self.sink, "gate": gate} if self.extras else {}
         n_rows = step.n_single if mma else T
         if n_rows > 0:
             per_block = kernels.DECODE_MMA_HEADS_PER_BLOCK if mma else 0
@@ -243,20 +243,17 @@ class GroupedQueryAttention(Mixer):
                 # pages arrive as TMA boxes.  Many splits (few rows, long contexts): the last block of a row
                 # and head group merges them; few splits: a second small kernel does, during which the
                 # output projection already loads its first weights (measured: 2 us a layer either way)
-                kernels.attention_decode_tma(*args, status=rt.status,
+                kernels.attention_decode_tma(*args, status=rt.status, **extra,
                                              merge_counters=rt.merge_counters if splits >= self.MERGE_IN_KERNEL_MIN_SPLITS else None)
             else:
-                if mma:
-                    kernels.attention_decode_mma(*args, status=rt.status)
-                else:
-                    kernels.attention_split(*args, status=rt.status, chunk=self.chunk, sink=self.sink, gate=gate)
+                (kernels.attention_decode_mma if mma else kernels.attention_split)(*args, status=rt.status, **extra)
         if mma and step.n_entries > step.n_single:
             # long portions: 128-token tiles on tcgen05 with the accumulators in tensor memory; short ones
             # (and page sizes a TMA box cannot take): 64-token tiles on mma.sync
             tc = step.max_q_len > 64 and kernels.attention_prefill_tc_fits(self.hd, g.page_size)
             fn = kernels.attention_prefill_tc if tc else kernels.attention_prefill_mma
             fn(q, cache.k, cache.v, o, step.cu_q, step.pos0, g.block_table, step.n_single,
-               step.n_entries - step.n_single, step.max_q_len, self.window or 0, self.scale, status=rt.status)
+               step.n_entries - step.n_single, step.max_q_len, self.window or 0, self.scale, status=rt.status, **extra)
 
     MERGE_IN_KERNEL_MIN_SPLITS = 8   # from here on the block that finishes last merges the splits itself
     FUSED_DECODE_MAX_ROWS = 48   # measured: 1.3-2.3 us a layer faster up to 32 rows, 1.6 us slower at 64
@@ -265,7 +262,7 @@ class GroupedQueryAttention(Mixer):
         """A step of single tokens only, on the path of the TMA decode kernel (bfloat16, head size 64 or 128,
         a page size it takes), with few enough rows that every block redoing the queries' norm and rotation
         costs less than a kernel of its own."""
-        return (not self.float_weights and not self.extras and (self.bias is None or self.own_kv)
+        return (not self.float_weights and (self.bias is None or self.own_kv)
                 and self.rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES
                 and kernels.attention_decode_tma_fits(self.hd, g.page_size)
                 and step.n_single == step.n_entries == step.n_tokens
@@ -315,7 +312,8 @@ class GroupedQueryAttention(Mixer):
                 self.q_norm_w, self.k_norm_w, self.norm_eps if self.norm_eps is not None else 1.0,
                 self.position.rotary_table(), write_kv=self.own_kv, status=rt.status,
                 merge_counters=rt.merge_counters if splits >= self.MERGE_IN_KERNEL_MIN_SPLITS else None,
-                bias=self.bias, q_temperature=self.position.query_temperature())
+                bias=self.bias, q_temperature=self.position.query_temperature(), chunk=self.chunk, sink=self.sink,
+                gate=gate)
         else:
             q = rt.scratch.get("attn_q", (rt.max_tokens, self.nq, self.hd), rt.dtype)[:T]
             args = (qkv, q, cache.k if self.own_kv else None, cache.v if self.own_kv else None, step.positions,

@@ -178,16 +178,26 @@ class MixtureOfExperts(FeedForward):
         idx, wts, _ = self.route(x, T, sort_into=(BM, src_row, row_w, pair_pos, *tiles))
         act = rt.scratch.get(f"moe_act_rows:{top}:{F}", (max_pairs, F), rt.dtype)[:pairs]
         rows = rt.scratch.get(f"moe_out_rows:{top}", (max_pairs, D), f32)[:pairs]
+        # the first product's rows an expert and its mode: with gates, gate and up rows in turn and the gated
+        # activation as the epilogue
+        F1, first = (2 * F, 2) if self.glu else (F, 0)
         if tc:
             xs = rt.scratch.get(f"moe_x_sorted:{top}", (max_pairs, D), rt.dtype)[:pairs]
             kernels.moe_gather_rows(xs, x, src_row)
-            kernels.moe_grouped_tc(act, xs, self.w_up, row_w, *tiles, F, D, F, 0, status=rt.status)
+            kernels.moe_grouped_tc(act, xs, self.w_up, row_w, *tiles, F1, D, F1, first, status=rt.status)
             kernels.moe_grouped_tc(rows, act, self.w_down, row_w, *tiles, D, F, F, 1, status=rt.status)
         else:
-            kernels.moe_grouped(act, x, src_row, self.w_up, F * self.w_up.stride(0), row_w, *tiles, F, D, BM, 0)
+            kernels.moe_grouped(act, x, src_row, self.w_up, F1 * self.w_up.stride(0), row_w, *tiles, F1, D, BM, first)
             kernels.moe_grouped(rows, act, None, self.w_down, F, row_w, *tiles, D, F, BM, 1)
         shared = None
-        if self.SF:
+        if self.SF and self.glu:
+            sa = rt.scratch.get(f"moe_shared_act:{self.SF}", (rt.max_tokens, self.SF), rt.dtype)[:T]
+            gu = rt.scratch.get(f"moe_shared_gate_up:{self.SF}", (rt.max_tokens, 2 * self.SF), rt.dtype)[:T]
+            rt.linear(gu, x, self.w_shared_up)
+            kernels.moe_dense_glu_act(sa, gu, None, 0, 1, self.SF, self._shared_gate(T))
+            shared = rt.scratch.get("moe_shared_out", (rt.max_tokens, D), rt.dtype)[:T]
+            rt.linear(shared, sa, self.w_shared_down)
+        elif self.SF:
             sa = rt.scratch.get(f"moe_shared_act:{self.SF}", (rt.max_tokens, self.SF), rt.dtype)[:T]
             rt.linear(sa, x, self.w_shared_up)
             kernels.moe_dense_act(sa, wts, 0, 1, self.SF)

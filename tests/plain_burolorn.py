@@ -385,3 +385,11 @@ def random_weights(cfg, seed, sharp=1.0):
     for i in range(len(cfg["layers"])):
         w[f"l{i}.mix.q"] = w[f"l{i}.mix.q"] * sharp
     return {k: v.to(torch.bfloat16).to(torch.float32) for k, v in w.items()}
+
+
+def greedy(cfg, weights, prompt, n):
+    """n tokens, each the largest logit after everything before it (ties: the lowest id)."""
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(torch.argmax(forward(cfg, weights, toks)[-1])))
+    return toks[len(prompt):]
