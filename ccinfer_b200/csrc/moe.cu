@@ -230,6 +230,38 @@ moe_dense_glu_act_kernel(T* __restrict__ act, int lda, const T* __restrict__ gu,
   }
 }
 
+// The same, bfloat16, eight columns a thread (F, shared, the widths and strides multiples of 8, 16-byte aligned
+// rows): the eight lie in one expert's columns and share its weight.  A block row per token, grid-strided.
+__global__ void __launch_bounds__(256)
+moe_dense_glu_act_vec_kernel(__nv_bfloat16* __restrict__ act, int lda, const __nv_bfloat16* __restrict__ gu, int ldg,
+                             const float* __restrict__ dense_w, const float* __restrict__ shared_gate, int sg_stride,
+                             int rows, int E, int F, int shared) {
+  ccb::pdl_begin();
+  const int width = E * F + shared;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= width) return;
+  const int e = c < E * F ? c / F : -1;
+  for (int t = blockIdx.y; t < rows; t += gridDim.y) {
+    float w;
+    if (e >= 0) w = dense_w[(size_t)t * E + e];
+    else w = shared_gate ? 1.f / (1.f + expf(-shared_gate[(size_t)t * sg_stride])) : 1.f;
+    uint4 res = make_uint4(0u, 0u, 0u, 0u);
+    if (w != 0.f) {
+      const uint4 gv = *reinterpret_cast<const uint4*>(gu + (size_t)t * ldg + c);
+      const uint4 uv = *reinterpret_cast<const uint4*>(gu + (size_t)t * ldg + width + c);
+      const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
+      const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uv);
+      __nv_bfloat162* rh = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 g = __bfloat1622float2(gh[i]), u = __bfloat1622float2(uh[i]);
+        rh[i] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x * w, g.y / (1.f + expf(-g.y)) * u.y * w);
+      }
+    }
+    *reinterpret_cast<uint4*>(act + (size_t)t * lda + c) = res;
+  }
+}
+
 }  // namespace
 
 CCB_API int ccb_moe_route(const float* logits, int ldl, const float* correction, int* idx, float* wts,
@@ -710,6 +742,14 @@ CCB_API int ccb_moe_dense_glu_act(void* act, int lda, const void* gu, int ldg, c
   if (rows <= 0) return 0;
   if (E < 0 || F <= 0 || shared < 0 || lda < E * F + shared || ldg < 2 * (E * F + shared)) return CCB_REFUSE_SIZE;
   if (E > 0 && dense_w == nullptr) return CCB_REFUSE_ARG;
+  const int width = E * F + shared;
+  if (dtype == CCB_BF16 && (E == 0 || F % 8 == 0) && shared % 8 == 0 && lda % 8 == 0 && ldg % 8 == 0 &&
+      ((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(gu)) & 15) == 0) {
+    const dim3 vgrid((width / 8 + 255) / 256, rows < 65535 ? rows : 65535);
+    ccb_launch(moe_dense_glu_act_vec_kernel, vgrid, dim3(256), 0, stream, (__nv_bfloat16*)act, lda,
+               (const __nv_bfloat16*)gu, ldg, dense_w, shared_gate, sg_stride, rows, E, F, shared);
+    return ccb_launch_status();
+  }
   const size_t total = (size_t)rows * (E * F + shared);
   const int blocks = (int)((total + 255) / 256 < 65535 * 8 ? (total + 255) / 256 : 65535 * 8);
   if (dtype == CCB_F32)

@@ -467,9 +467,9 @@ def conv_state_update(proj, offsets, conv_state, taps: int, cu_q, state_slot, n_
 def conv_rows(out, rows, w, taps: int, C: int, state, entry_of_token, cu_q, state_slot, n_entries: int,
               values=None, status=None) -> None:
     """A short causal convolution over time on the first ``C`` columns of a step's rows: out[t, c] = sum_j
-    w[c, j] * u[t - taps + 1 + j, c] over the request's rows in order, those before the step's first one taken from
-    ``state`` [slots, taps - 1, C] (compute type; zeros for a new request).  ``w`` float [C, taps], or None with
-    taps 1 for no convolution.  A request that brings one token has its state moved on here; for the others call
+    w[j, c] * u[t - taps + 1 + j, c] over the request's rows in order, those before the step's first one taken from
+    ``state`` [slots, taps - 1, C] (compute type; zeros for a new request).  ``w`` float [taps, C] (tap-major), or None
+    with taps 1 for no convolution.  A request that brings one token has its state moved on here; for the others call
     ``conv_state_rows`` afterwards.  ``values`` = (v_off, heads, head_size, real_size, v_first, lam): the columns
     from v_off on are value heads of ``head_size`` coordinates of which ``real_size`` are real; with ``lam`` None
     the results are also left in ``v_first`` [T, heads * real_size], else out = (1 - lam) out + lam v_first
@@ -477,7 +477,7 @@ def conv_rows(out, rows, w, taps: int, C: int, state, entry_of_token, cu_q, stat
     _cuda(w, state, entry_of_token, cu_q, state_slot, status)
     T = rows.shape[0]
     assert rows.dtype == out.dtype and rows.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == T
-    assert w is None or (w.dtype == torch.float32 and w.shape == (C, taps))
+    assert w is None or (w.dtype == torch.float32 and w.shape == (taps, C))
     assert state is None or (state.dtype == rows.dtype and tuple(state.shape[1:]) == (taps - 1, C))
     vmode, v_off, vh, vhd, vd, v_first, lam = 0, 0, 0, 0, 0, None, None
     if values is not None:

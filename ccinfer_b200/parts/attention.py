@@ -214,8 +214,9 @@ class GroupedQueryAttention(Mixer):
             self.k_norm_w = norm_w("k_norm") if self.own_kv else None
             self.norm_eps = self.qk_norm_eps * self.qk_dim / hd
         if self.taps:
+            # tap-major for the kernel: [taps, q | k | v channels]
             self.conv_w = torch.cat([qk("q_conv", self.nq), qk("k_conv", self.nkv),
-                                     laid_out(fetch(n["v_conv"]), self.nkv, self.v_dim)], dim=0).float().contiguous()
+                                     laid_out(fetch(n["v_conv"]), self.nkv, self.v_dim)], dim=0).float().t().contiguous()
         if "sink" in n:
             self.sink = fetch(n["sink"]).float().contiguous()
         if self.value_mix is not None and self.value_mix[0] == "mix":

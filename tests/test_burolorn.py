@@ -193,7 +193,8 @@ def test_short_convolution_kernel(dtype, taps, C):
         out = torch.empty_like(rows)
         cu_d, eot_d = torch.from_numpy(cu).to(dev), torch.from_numpy(eot).to(dev)
         slot_d = torch.tensor(order, dtype=torch.int32, device=dev)
-        kernels.conv_rows(out, rows, w.to(dev), taps, C, state if taps > 1 else None, eot_d, cu_d, slot_d, len(order))
+        kernels.conv_rows(out, rows, w.t().contiguous().to(dev), taps, C, state if taps > 1 else None, eot_d, cu_d,
+                          slot_d, len(order))
         if taps > 1:
             kernels.conv_state_rows(rows, taps, C, state, cu_d, slot_d, n_single, len(order) - n_single)
         for i, s in enumerate(order):
@@ -210,13 +211,15 @@ def test_short_convolution_kernel(dtype, taps, C):
 
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_short_convolution_keeps_and_mixes_values(dtype):
-    """Value heads of 5 real coordinates laid out in 8: the first layer's results are kept as rows of real
-    coordinates, a later layer's are mixed with them; the other channels and the padding are left alone."""
+@pytest.mark.parametrize("heads,hd,vd,v_off", [(3, 8, 5, 16), (2, 32, 24, 64), (1, 16, 16, 8)])
+def test_short_convolution_keeps_and_mixes_values(dtype, heads, hd, vd, v_off):
+    """Value heads of 5 real coordinates laid out in 8 (and sizes that the kernel of eight channels a thread
+    takes): the first layer's results are kept as rows of real coordinates, a later layer's are mixed with them;
+    the other channels and the padding are left alone."""
     from ccinfer_b200 import kernels
     dev = "cuda"
     g = torch.Generator().manual_seed(5)
-    T, taps, heads, hd, vd, v_off = 6, 2, 3, 8, 5, 16
+    T, taps = 6, 2
     C = v_off + heads * hd
     w = torch.randn(C, taps, generator=g)
     u1, u2 = torch.randn(T, C, generator=g).to(dtype), torch.randn(T, C, generator=g).to(dtype)
@@ -228,7 +231,7 @@ def test_short_convolution_keeps_and_mixes_values(dtype):
     y1, y2 = torch.empty(T, C, dtype=dtype, device=dev), torch.empty(T, C, dtype=dtype, device=dev)
     for u, y, l in ((u1, y1, None), (u2, y2, lam.to(dev))):
         state = torch.zeros(1, taps - 1, C, dtype=dtype, device=dev)
-        kernels.conv_rows(y, u.to(dev), w.to(dev), taps, C, state, eot, cu, slot, 1,
+        kernels.conv_rows(y, u.to(dev), w.t().contiguous().to(dev), taps, C, state, eot, cu, slot, 1,
                           values=(v_off, heads, hd, vd, first, l))
     c1, c2 = plain.short_conv(u1.double(), w.double()), plain.short_conv(u2.double(), w.double())
     tol = 1e-5 if dtype == torch.float32 else 3e-2
