@@ -5,7 +5,7 @@
      "token_side": {"dim": n}}                           (optional: a per-layer token input of n columns)
 
 The mixer ``attention``: heads, kv_heads, dim (query/key size of a head), vdim (value size), scale; ``conv`` (taps
-of a short causal convolution on q, k and v; absent or null: none); ``rot`` {dims, base} (rotate-half over the
+of a short causal convolution on q, k and v; absent, null or 0: none); ``rot`` {dims, base} (rotate-half over the
 first ``dims`` coordinates; absent: no rotation); ``mask`` {size} (a query sees the keys of its own run of ``size``
 positions; absent: every earlier key); ``v_mix`` (true: values are mixed with those of the first such layer).
 
@@ -111,7 +111,7 @@ class BurolornConfig:
             dim, vdim = _get(mj, "dim", mw, int), _get(mj, "vdim", mw, int)
             if heads % kv_heads:
                 raise ModelConfigInvalid(f"config.json: {mw}: {heads} heads are not a multiple of {kv_heads} kv_heads")
-            conv = _get(mj, "conv", mw, int) if mj.get("conv") is not None else 0
+            conv = _get(mj, "conv", mw, int) if mj.get("conv") not in (None, 0) else 0
             rot_dims, rot_base = 0, 10000.0
             if mj.get("rot") is not None:
                 rot_dims, rot_base = _get(mj["rot"], "dims", mw + ".rot", int), _get(mj["rot"], "base", mw + ".rot", float)
