@@ -690,3 +690,88 @@ def test_the_programs_as_a_user_calls_them(models, tmp_path):
                 seen[e["id"]] += len(e["tokens"])
         assert len(rows) == sum(len(x) for x in reqs.values())
         compare(rows, dref, dtype, "trace_run " + dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU: configurations drawn at random
+# ---------------------------------------------------------------------------------------------
+def draw_config(seed):
+    """Every size, option and constant that a configuration may state, drawn at random: widths and vocabularies
+    that are multiples of nothing, any number of heads and groups, key and value sizes from 4 to 130 (often the
+    sizes of the tensor-core kernels), any order of dense, mixture and absent feed-forwards, taps from none to
+    five, rotations of none, a part or all of a head, runs from one position to beyond the prompts, layers that
+    mix values or not, routers with and without groups, scales and shared experts, with and without a side
+    input and a scale of the logits.  Key-value heads and the value size are one per model (mixed values must
+    have one shape)."""
+    rng = np.random.RandomState(7000 + seed)
+    width = int(rng.choice([int(rng.randint(20, 150)), 64, 96, 128]))
+    vocab = int(rng.randint(40, 260))
+    G = int(rng.choice([1, 2, 3, 4]))
+    fast = rng.rand() < 0.5
+    vdim = int(rng.choice([64, 128])) if fast else int(rng.randint(2, 66)) * 2
+    layers = []
+    for _ in range(int(rng.randint(1, 6))):
+        H = G * int(rng.choice([1, 2, 3, 4, 6]))
+        if fast:
+            dim = int(rng.choice([d for d in (32, 48, 64, 112, 128) if -(-max(d, vdim) // 16) * 16 in (64, 128)]))
+        else:
+            dim = int(rng.randint(2, 66)) * 2
+        rot = None
+        if rng.rand() < 0.8:
+            rot = (int(rng.choice([2, dim // 2 // 2 * 2 or 2, dim])), float(rng.choice([20.0, 1000.0, 50000.0])))
+            rot = (min(rot[0], dim), rot[1])
+        mixer = plain.attn(H, G, dim, vdim, float(dim ** -0.5 * rng.uniform(0.7, 1.5)),
+                           conv=[None, 1, 2, 3, 4, 5][int(rng.randint(6))], rot=rot,
+                           chunk=[None, 1, int(rng.randint(2, 20)), int(rng.randint(20, 90)), 500][int(rng.randint(5))],
+                           v_mix=bool(rng.rand() < 0.6))
+        kind = int(rng.randint(4))
+        if kind == 0:
+            mlp = None
+        elif kind == 1:
+            mlp = plain.dense(int(rng.randint(8, 120)))
+        else:
+            count = int(rng.choice([1, 2, 3, 4]))
+            per = int(rng.randint(1, 5))
+            keep = int(rng.randint(1, count + 1))
+            top = int(rng.randint(1, per * keep + 1))
+            mlp = plain.experts(count * per, top, int(rng.randint(1, 9)) * 8,
+                                groups=(count, keep) if rng.rand() < 0.7 or keep < count else None,
+                                scale=float(rng.uniform(0.5, 3.0)) if rng.rand() < 0.6 else None,
+                                shared=int(rng.randint(1, 9)) * 8 if rng.rand() < 0.6 else None)
+        layers.append((mixer, mlp))
+    cfg = plain.model(vocab, width, float(rng.choice([1e-5, 1e-6])), layers,
+                      side=int(rng.randint(1, 20)) if rng.rand() < 0.6 else None,
+                      logit_scale=float(rng.choice([0.5, 2.0, 1.7])) if rng.rand() < 0.6 else None)
+    page = int(rng.choice([8, 16, 32] if fast else [4, 8, 16]))
+    lengths = [1, 2] + [int(rng.randint(3, 140)) for _ in range(5)] + ([int(rng.randint(140, 300))] if fast else [])
+    return cfg, page, lengths
+
+
+FUZZ_SEEDS = int(os.environ.get("CCB_FUZZ_SEEDS", "10"))
+
+
+@gpu
+@pytest.mark.parametrize("seed", range(FUZZ_SEEDS))
+def test_random_configurations(tmp_path, seed):
+    """A mixed trace over four request slots with a pool that is just large enough, then every request whole, in
+    32-bit and in bfloat16, against the plain implementation."""
+    cfg, page, lengths = draw_config(seed)
+    for dtype in ("float32", "bfloat16"):
+        d = str(tmp_path / dtype)
+        cfg, w = write_model(d, cfg=cfg, seed=seed, sharp=SHARP[dtype])
+        reqs = requests_of(cfg, lengths, seed)
+        ref = {rid: plain.forward(cfg, w, t).numpy() for rid, t in reqs.items()}
+        steps = helpers.trace_mixed(reqs, max_live=4, seed=seed)
+        whole = helpers.trace_whole(reqs)
+        pool = max(helpers.max_live_tokens(steps, round_to=max(64, page)),
+                   helpers.max_live_tokens(whole, round_to=max(64, page)))
+        eng = engine_of(d, dtype, page, pool, max_requests=4)
+        for trace in (steps, whole):
+            rows = helpers.replay(eng, trace)
+            assert len(rows) == sum(len(t) for t in reqs.values())
+            what = f"random configuration {seed} {dtype}: {json.dumps(cfg)}"
+            if dtype == "float32":   # (drawn constants reach further than the fixed configurations': 32-bit sums
+                helpers.compare(rows, ref, 1e-4, what)   # against 64-bit ones lie up to 5e-5 apart, however cut)
+            else:
+                compare(rows, ref, dtype, what)
+        assert all(p.used_pages == 0 for p in eng.cache.pools)
