@@ -16,6 +16,7 @@ their kernels, is the runner that this class registers there.
 from __future__ import annotations
 
 import dataclasses
+import gc
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
@@ -472,8 +473,18 @@ class Engine:
             self.rt.scratch.freeze()  # ... and none may move once a graph holds its address
             graph = torch.cuda.CUDAGraph()
             own0, lib0 = kernels.counters.own, kernels.counters.library
-            with torch.cuda.graph(graph):
-                out = self._forward(step)
+            # A capture fails when anything frees device or pinned memory meanwhile, and the collector may do that
+            # at any allocation (an engine that is no longer used, with its graphs and buffers, is cyclic
+            # garbage): what is garbage goes now, and the collector rests until the capture has ended.
+            collecting = gc.isenabled()
+            gc.collect()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    out = self._forward(step)
+            finally:
+                if collecting:
+                    gc.enable()
             self._graphs[bucket] = (graph, out, kernels.counters.own - own0, kernels.counters.library - lib0)
             if self._state:
                 # the eager run WAS this step: keys and values may be written twice, a state that is carried
