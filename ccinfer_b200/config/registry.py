@@ -52,6 +52,11 @@ def _builtin():
         from ..architectures import burolorn
         from .burolorn import BurolornConfig
         register_architecture("Burolorn", BurolornConfig.from_json, burolorn.build_plan)
+    if "Gevovik" not in _REGISTRY:
+        from ..architectures import gevovik
+        from .gevovik import GevovikConfig
+        register_architecture("Gevovik", GevovikConfig.from_json, gevovik.build_plan,
+                              complete_config=lambda cfg, shapes: cfg.with_shapes(shapes))
     if "Dufizen" not in _REGISTRY:
         from ..architectures import dufizen
         from .dufizen import DufizenConfig

@@ -36,11 +36,13 @@ GROUPS = {
         "short_conv.cu",
         "delta_rule.cu",
         "linear_attention.cu",
+        "ssm.cu",
         "latent_attention.cu",
         "moe.cu",
         "moe_tcgen05.cu",
         "attention_generic.cu",
         "attention_split.cu",
+        "attention_talking.cu",
         "attention_decode_mma.cu",
         "attention_decode_tma.cu",
         "attention_prefill_mma.cu",

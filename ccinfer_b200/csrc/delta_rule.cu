@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(kRecThreads)
 delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
                         const float* __restrict__ gg, const float* __restrict__ bb, float* __restrict__ state,
                         float* __restrict__ out, const int* __restrict__ cu_q, const int* __restrict__ state_slot,
-                        int G, int H, int dk, int dv, int tch) {
+                        int G, int H, int dk, int dv, int tch, int g_dk) {
   ccb::pdl_begin();
   constexpr int DP = R * kLanes;
   constexpr int COLS = kCols * C;   // columns of S per block
@@ -316,7 +316,8 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
       const size_t row = (size_t)(r0 + t0 + tt);
       cp_async4(base + tt * DP + r, qn + (row * G + kvh) * dk + r);
       cp_async4(base + tch * DP + tt * DP + r, kn + (row * G + kvh) * dk + r);
-      cp_async4(base + 2 * tch * DP + tt * DP + r, gg + (row * H + head) * dk + r);
+      // (g_dk = 1: one decay per head and token, the same for every key channel)
+      cp_async4(base + 2 * tch * DP + tt * DP + r, gg + (row * H + head) * g_dk + (g_dk > 1 ? r : 0));
     }
     float* sv = base + 3 * tch * DP;
     for (int i = threadIdx.x; i < cnt * COLS; i += kRecThreads) {
@@ -325,7 +326,7 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
       if (gc < dv) cp_async4(sv + i, vv + ((size_t)(r0 + t0 + tt) * H + head) * dv + gc);
     }
     float* sb = sv + tch * COLS;
-    if (DELTA)
+    if (DELTA || bb != nullptr)
       for (int i = threadIdx.x; i < cnt; i += kRecThreads) cp_async4(sb + i, bb + (size_t)(r0 + t0 + i) * H + head);
     cp_async_commit();
   };
@@ -356,7 +357,7 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
       Rows<R>::load(base + tt * DP, lane, qr);
       Rows<R>::load(base + tch * DP + tt * DP, lane, kr);
       Rows<R>::load(base + 2 * tch * DP + tt * DP, lane, gr);
-      const float beta = DELTA ? sb[tt] : 1.f;
+      const float beta = (DELTA || bb != nullptr) ? sb[tt] : 1.f;   // (plain form with bb: the write is beta * v)
       constexpr int P = R < 4 ? R : 4;   // partial sums per lane
       float kqp[P];
 #pragma unroll
@@ -391,7 +392,7 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
       for (int c = 0; c < C; ++c) dqq[c] = lanes_sum(dqq[c]);
 #pragma unroll
       for (int c = 0; c < C; ++c) {
-        const float u = DELTA ? beta * (sv[tt * COLS + cl * C + c] - dkk[c]) : sv[tt * COLS + cl * C + c];
+        const float u = DELTA ? beta * (sv[tt * COLS + cl * C + c] - dkk[c]) : beta * sv[tt * COLS + cl * C + c];
 #pragma unroll
         for (int i = 0; i < R; ++i) S[c][i] = fmaf(kr[i], u, S[c][i]);
         if (lane == c % kLanes && col0 + c < dv)
@@ -543,21 +544,22 @@ CCB_API int ccb_conv_state_update(const void* proj, int ld, int oq, int ok, int 
 template <int R, int C, bool DELTA>
 static void launch_recurrence(const float* qn, const float* kn, const float* vv, const float* gg, const float* bb,
                               float* state, float* out, const int* cu_q, const int* state_slot, int n_entries, int G,
-                              int H, int dk, int dv, cudaStream_t stream) {
+                              int H, int dk, int dv, cudaStream_t stream, int g_dk) {
   constexpr int DP = R * kLanes, COLS = kCols * C;
   const int tch = DP <= 128 ? 16 : 8;
   const size_t smem = (size_t)2 * (tch * (3 * DP + COLS) + ((tch + 3) & ~3)) * sizeof(float);
   cudaFuncSetAttribute(delta_recurrence_kernel<R, C, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid((dv + COLS - 1) / COLS, H, n_entries);
   ccb_launch(delta_recurrence_kernel<R, C, DELTA>, grid, dim3(kRecThreads), smem, stream, qn, kn, vv, gg, bb, state, out,
-             cu_q, state_slot, G, H, dk, dv, tch);
+             cu_q, state_slot, G, H, dk, dv, tch, g_dk);
 }
 
 template <bool DELTA>
 static int pick_recurrence(const float* qn, const float* kn, const float* vv, const float* gg, const float* bb,
                            float* state, float* out, const int* cu_q, const int* state_slot, int n_entries, int G,
-                           int H, int dk, int dv, cudaStream_t stream) {
+                           int H, int dk, int dv, cudaStream_t stream, bool head_decay = false) {
   if (n_entries <= 0) return 0;
+  const int g_dk = head_decay ? 1 : dk;
   if (G <= 0 || H <= 0 || H % G || dk <= 0 || dk > 256 || dv <= 0) return CCB_REFUSE_SIZE;
   int R = 1;
   while (R * kLanes < dk) R *= 2;
@@ -567,7 +569,7 @@ static int pick_recurrence(const float* qn, const float* kn, const float* vv, co
   // fewer warps per SM.  Sixteen lanes a column (twice the warps, one shuffle more per sum) were no faster
   // either (1.03 ms).
 #define CCB_REC(RR) \
-  launch_recurrence<RR, 1, DELTA>(qn, kn, vv, gg, bb, state, out, cu_q, state_slot, n_entries, G, H, dk, dv, stream)
+  launch_recurrence<RR, 1, DELTA>(qn, kn, vv, gg, bb, state, out, cu_q, state_slot, n_entries, G, H, dk, dv, stream, g_dk)
   switch (R) {
     case 1: CCB_REC(1); break;
     case 2: CCB_REC(2); break;
@@ -592,6 +594,17 @@ CCB_API int ccb_gated_linear_recurrence(const float* qn, const float* kn, const 
                                         int n_entries, int G, int H, int dk, int dv, cudaStream_t stream) {
   return pick_recurrence<false>(qn, kn, vv, gg, nullptr, state, out, cu_q, state_slot, n_entries, G, H, dk, dv,
                                 stream);
+}
+
+// The plain recurrence with ONE decay per head and token and a step size on the write (a selective state space
+// in its recurrent form):  S <- a_t S + (dt_t v_t-row) ... i.e.  S <- a_t S + k_t (dt_t v_t)^T,  o_t = S^T q_t.
+// a and dt float [T, H]; q and k have G groups of dk channels.
+CCB_API int ccb_ssm_recurrence(const float* qn, const float* kn, const float* vv, const float* a, const float* dt,
+                               float* state, float* out, const int* cu_q, const int* state_slot, int n_entries,
+                               int G, int H, int dk, int dv, cudaStream_t stream) {
+  if (a == nullptr || dt == nullptr) return CCB_REFUSE_ARG;
+  return pick_recurrence<false>(qn, kn, vv, a, dt, state, out, cu_q, state_slot, n_entries, G, H, dk, dv, stream,
+                                true);
 }
 
 template <typename T, bool SILU>

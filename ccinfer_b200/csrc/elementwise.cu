@@ -340,3 +340,182 @@ CCB_API int ccb_gelu_gate_rows(void* g, int ldg, const void* table, int ldt, int
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Token embedding times a constant, plus a row of a second table chosen by the pair (previous token, token):
+//   h[t, :] = float(table[id, :]) * scale + float(pair_table[row, :])
+//   row = (prev * mul_prev + id * mul_cur) mod buckets, or `buckets` (the table's last row) at position 0.
+// The previous token of a portion's first token is what the request's slot of `prev_token` holds; the others find
+// theirs in the step.  `rows` (optional): the same values in the storage type, for a block that reads the stream
+// itself.  embed_pair_commit then stores each request's last token of the step (a kernel of its own: the first
+// token's block of a request may run after the last one's).
+template <typename T>
+__global__ void embed_pair_kernel(float* __restrict__ h, T* __restrict__ rows, const T* __restrict__ table,
+                                  const T* __restrict__ pair_table, const int* __restrict__ ids,
+                                  const int* __restrict__ positions, const int* __restrict__ entry_of_token,
+                                  const int* __restrict__ cu_q, const int* __restrict__ state_slot,
+                                  const int* __restrict__ prev_token, float scale, int buckets, int mul_prev,
+                                  int mul_cur, int D, int V, const int* __restrict__ pending, int n_pending,
+                                  int* status) {
+  ccb::pdl_begin();
+  const int t = blockIdx.x;
+  float* out = h + (size_t)t * D;
+  T* out2 = rows ? rows + (size_t)t * D : nullptr;
+  const int e = entry_of_token[t];
+  int id = ids[t];
+  if (id < 0 && pending != nullptr && -1 - id < n_pending) id = pending[-1 - id];
+  if (e < 0 || id < 0 || id >= V) {
+    if (e >= 0 && threadIdx.x == 0) set_status(status, CCB_ST_BAD_TOKEN);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      out[d] = 0.f;
+      if (out2) out2[d] = from_f32<T>(0.f);
+    }
+    return;
+  }
+  const T* pr = nullptr;
+  if (pair_table != nullptr) {
+    int row = buckets;
+    if (positions[t] > 0) {
+      int prev;
+      if (t > cu_q[e]) {
+        prev = ids[t - 1];
+      } else {
+        const int slot = state_slot[e];
+        prev = slot >= 0 ? prev_token[slot] : 0;
+      }
+      if (prev < 0 || prev >= V) {
+        if (threadIdx.x == 0) set_status(status, CCB_ST_BAD_TOKEN);
+        prev = 0;
+      }
+      row = (int)(((long long)prev * mul_prev + (long long)id * mul_cur) % buckets);
+    }
+    pr = pair_table + (size_t)row * D;
+  }
+  const T* er = table + (size_t)id * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float v = to_f32(er[d]) * scale;
+    if (pr) v += to_f32(pr[d]);
+    out[d] = v;
+    if (out2) out2[d] = from_f32<T>(v);
+  }
+}
+
+__global__ void embed_pair_commit_kernel(const int* __restrict__ ids, const int* __restrict__ cu_q,
+                                         const int* __restrict__ state_slot, int* __restrict__ prev_token,
+                                         int n_entries, int n_slots, const int* __restrict__ pending, int n_pending) {
+  ccb::pdl_begin();
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n_entries) return;
+  const int slot = state_slot[e];
+  const int n = cu_q[e + 1] - cu_q[e];
+  if (slot < 0 || slot >= n_slots || n <= 0) return;
+  int id = ids[cu_q[e + 1] - 1];
+  if (id < 0 && pending != nullptr && -1 - id < n_pending) id = pending[-1 - id];
+  prev_token[slot] = id;
+}
+
+CCB_API int ccb_embed_pair(float* h, void* rows, const void* table, const void* pair_table, const int* ids,
+                           const int* positions, const int* entry_of_token, const int* cu_q, const int* state_slot,
+                           int* prev_token, float scale, int buckets, int mul_prev, int mul_cur, int T_, int n_entries,
+                           int n_slots, int D, int V, int dtype, const int* pending, int n_pending, int* status,
+                           cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (D <= 0 || V <= 0 || (pair_table != nullptr && (buckets <= 0 || mul_prev < 0 || mul_cur < 0)))
+    return CCB_REFUSE_SIZE;
+  if (pair_table != nullptr && prev_token == nullptr) return CCB_REFUSE_ARG;
+  const int threads = D >= 1024 ? 256 : 128;
+  if (dtype == CCB_F32)
+    ccb_launch(embed_pair_kernel<float>, T_, threads, 0, stream, h, (float*)rows, (const float*)table,
+               (const float*)pair_table, ids, positions, entry_of_token, cu_q, state_slot, (const int*)prev_token, scale,
+               buckets, mul_prev, mul_cur, D, V, pending, n_pending, status);
+  else if (dtype == CCB_BF16)
+    ccb_launch(embed_pair_kernel<__nv_bfloat16>, T_, threads, 0, stream, h, (__nv_bfloat16*)rows,
+               (const __nv_bfloat16*)table, (const __nv_bfloat16*)pair_table, ids, positions, entry_of_token, cu_q,
+               state_slot, (const int*)prev_token, scale, buckets, mul_prev, mul_cur, D, V, pending, n_pending, status);
+  else
+    return CCB_REFUSE_DTYPE;
+  int rc = ccb_launch_status();
+  if (rc != 0 || pair_table == nullptr || n_entries <= 0) return rc;
+  ccb_launch(embed_pair_commit_kernel, (n_entries + 127) / 128, 128, 0, stream, ids, cu_q, state_slot, prev_token,
+             n_entries, n_slots, pending, n_pending);
+  return ccb_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// act = relu(x)^2, elementwise (the activation of a feed-forward without a gate).
+template <typename T>
+__global__ void relu_squared_kernel(T* __restrict__ act, const T* __restrict__ x, size_t total) {
+  ccb::pdl_begin();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = fmaxf(to_f32(x[i]), 0.f);
+    act[i] = from_f32<T>(v * v);
+  }
+}
+
+__global__ void relu_squared_bf16x8_kernel(uint4* __restrict__ act, const uint4* __restrict__ x, size_t total8) {
+  ccb::pdl_begin();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 a = x[i];
+    const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 f = __bfloat1622float2(ah[e]);
+      f.x = fmaxf(f.x, 0.f);
+      f.y = fmaxf(f.y, 0.f);
+      oh[e] = __floats2bfloat162_rn(f.x * f.x, f.y * f.y);
+    }
+    act[i] = o;
+  }
+}
+
+CCB_API int ccb_relu_squared(void* act, const void* x, long long total, int dtype, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const int threads = 256;
+  if (dtype == CCB_BF16 && total % 8 == 0 &&
+      ((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(x)) & 15) == 0) {
+    const size_t total8 = (size_t)total / 8;
+    const size_t want = (total8 + threads - 1) / threads;
+    ccb_launch(relu_squared_bf16x8_kernel, (int)(want < 148 * 32 ? want : 148 * 32), threads, 0, stream, (uint4*)act,
+               (const uint4*)x, total8);
+    return ccb_launch_status();
+  }
+  const size_t want = ((size_t)total + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
+  if (dtype == CCB_F32)
+    ccb_launch(relu_squared_kernel<float>, blocks, threads, 0, stream, (float*)act, (const float*)x, (size_t)total);
+  else if (dtype == CCB_BF16)
+    ccb_launch(relu_squared_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)act,
+               (const __nv_bfloat16*)x, (size_t)total);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// out = sa * a + sb * b, elementwise in float (two mixers side by side, each with a constant factor).
+template <typename T>
+__global__ void scaled_sum_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, float sa,
+                                  float sb, size_t total) {
+  ccb::pdl_begin();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<T>(fmaf(sa, to_f32(a[i]), sb * to_f32(b[i])));
+}
+
+CCB_API int ccb_scaled_sum(void* out, const void* a, const void* b, float sa, float sb, long long total, int dtype,
+                           cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const int threads = 256;
+  const size_t want = ((size_t)total + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
+  if (dtype == CCB_F32)
+    ccb_launch(scaled_sum_kernel<float>, blocks, threads, 0, stream, (float*)out, (const float*)a, (const float*)b, sa,
+               sb, (size_t)total);
+  else if (dtype == CCB_BF16)
+    ccb_launch(scaled_sum_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)out,
+               (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, sa, sb, (size_t)total);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}

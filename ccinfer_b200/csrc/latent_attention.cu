@@ -188,7 +188,7 @@ latent_attention_kernel(const float* __restrict__ qa, const T* __restrict__ cach
     }
   }
   if (!live) return;
-  const float g = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * ldg + head])));
+  const float g = gate ? 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * ldg + head]))) : 1.0f;   // (no gate: the factor is one)
   const float f = g / l;
   T* dst = out + ((size_t)t * H + head) * R;
 #pragma unroll
@@ -437,7 +437,7 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
       if (!row_ok[rt][hh]) continue;
       const size_t row = (size_t)row_t[rt][hh] * H + row_h[rt][hh];
       if (num_splits == 1) {
-        const float g = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)row_t[rt][hh] * ldg + row_h[rt][hh]])));
+        const float g = gate ? 1.0f / (1.0f + expf(-to_f32(gate[(size_t)row_t[rt][hh] * ldg + row_h[rt][hh]]))) : 1.0f;
         const float f = g / l[rt][hh];
 #pragma unroll
         for (int i = 0; i < NPW; ++i) {
@@ -495,7 +495,7 @@ latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict_
 #pragma unroll
     for (int i = 0; i < 2; ++i) e[i] = ms[i] == -CUDART_INF_F ? 0.f : expf(ms[i] - M);
     const float L = warp_sum(ls[0] * e[0] + ls[1] * e[1]);
-    const float g = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * ldg + h])));
+    const float g = gate ? 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * ldg + h]))) : 1.0f;
 #pragma unroll
     for (int i = 0; i < 2; ++i)
       if (lane + 32 * i < num_splits) f[lane + 32 * i] = e[i] * g / L;

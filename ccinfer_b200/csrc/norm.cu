@@ -298,6 +298,7 @@ postnorm_residual_kernel(T* __restrict__ y, float* __restrict__ h, const T* __re
     if (ar) v += ar[d];
     if (dr || ar) hr[d] = v;
     ss2 += v * v;
+    if (y != nullptr && w_next == nullptr) y[(size_t)r * D + d] = from_f32<T>(v);   // the stream's own rows
   }
   if (w_next == nullptr) return;
   ss2 = block_sum<kNormThreads>(ss2, red);
@@ -361,6 +362,7 @@ postnorm_residual_vec_kernel(T* __restrict__ y, float* __restrict__ h, const T* 
       if (dr || ar) Vec4<float>::store(hr + 4 * i, x);
       v[j] = x;
       ss2 += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+      if (y != nullptr && w_next == nullptr) Vec4<T>::store(y + (size_t)r * D + 4 * i, x);   // the stream's own rows
     }
   }
   if (w_next == nullptr) return;

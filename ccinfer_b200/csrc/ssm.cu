@@ -1,0 +1,197 @@
+// A selective state space mixer (the recurrent form of state-space duality): what surrounds its recurrence.
+//
+// The input projection's rows are laid out [z | x | B | C | dt]: a gate z and an input x of `inner` = H P channels,
+// G groups of N channels each for B and C, and one step-size logit per head.  x, B and C pass a short causal
+// convolution per channel (with bias) and silu; dt = softplus(dt + dt_bias); a = exp(-exp(A_log_h) dt).  Head h
+// (with group g = h / (H / G)) then runs
+//     S <- a_t S + B_t (dt_t x_t)^T        S [N, P], float, carried from token to token per request
+//     y_t = S^T C_t + D_h x_t
+// (the recurrence itself is ccb_ssm_recurrence in delta_rule.cu).  y is multiplied by silu(z), RMS-normed in
+// `parts` equal slices of the inner channels, each by its own root mean square, times a weight per channel.
+//
+//   ssm_prepare        a thread per (token, channel): convolution (earlier rows from the step or from the request's
+//                      convolution state, which holds its last taps - 1 projected rows), bias, silu; float rows of x,
+//                      B, C, and per (token, head) dt and a
+//   conv_state_shift   a thread per (request, channel): the last taps - 1 projected rows of each request's portion
+//                      become its convolution state (run after ssm_prepare has read the old one)
+//   ssm_gate_norm      a block per (token, slice): (o + D x) silu(z), its root mean square, the weight
+//
+// Everything after the projection is float; the projection's rows and the convolution state are of the storage type.
+#include "common.cuh"
+
+using namespace ccb;
+
+namespace {
+
+__device__ __forceinline__ float sigmoid_acc(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float softplus_acc(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// proj [T, ld]: the convolved channels (x | B | C, `C` of them) start at column ox, dt at odt.
+// conv_w [taps, C] (tap-major), conv_b [C]; conv_state [slots, taps - 1, C].
+template <typename T>
+__global__ void ssm_prepare_kernel(const T* __restrict__ proj, int ld, int ox, int odt,
+                                   const float* __restrict__ conv_w, const float* __restrict__ conv_b, int taps,
+                                   const T* __restrict__ conv_state, const float* __restrict__ A_log,
+                                   const float* __restrict__ dt_bias, const int* __restrict__ entry_of_token,
+                                   const int* __restrict__ cu_q, const int* __restrict__ state_slot,
+                                   float* __restrict__ xs, float* __restrict__ bs, float* __restrict__ cs,
+                                   float* __restrict__ dts, float* __restrict__ as, int rows, int H, int P, int G, int N) {
+  ccb::pdl_begin();
+  const int inner = H * P, gn = G * N;
+  const int C = inner + 2 * gn;
+  const int per_row = C + H;
+  const size_t total = (size_t)rows * per_row;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(i / per_row), c = (int)(i - (size_t)t * per_row);
+    const int e = entry_of_token[t];
+    if (c >= C) {   // a head's step size and decay
+      const int h = c - C;
+      float dt = 0.f, a = 1.f;
+      if (e >= 0) {
+        dt = softplus_acc(to_f32(proj[(size_t)t * ld + odt + h]) + dt_bias[h]);
+        a = expf(-expf(A_log[h]) * dt);
+      }
+      dts[(size_t)t * H + h] = dt;
+      as[(size_t)t * H + h] = a;
+      continue;
+    }
+    float v = 0.f;
+    if (e >= 0) {
+      const int r0 = cu_q[e];
+      const int slot = state_slot[e];
+      float acc = conv_b ? conv_b[c] : 0.f;
+      for (int j = 0; j < taps; ++j) {
+        const int src = t - (taps - 1) + j;   // the row this tap reads
+        float u;
+        if (src >= r0) u = to_f32(proj[(size_t)src * ld + ox + c]);
+        else u = slot >= 0 ? to_f32(conv_state[((size_t)slot * (taps - 1) + (src - r0 + taps - 1)) * C + c]) : 0.f;
+        acc = fmaf(conv_w[(size_t)j * C + c], u, acc);
+      }
+      v = acc * sigmoid_acc(acc);
+    }
+    if (c < inner) xs[(size_t)t * inner + c] = v;
+    else if (c < inner + gn) bs[(size_t)t * gn + (c - inner)] = v;
+    else cs[(size_t)t * gn + (c - inner - gn)] = v;
+  }
+}
+
+// state [slots, taps - 1, C] <- the last taps - 1 of (its old rows, then the request's rows of this step).
+// A thread owns one (request, channel) and walks the state's rows upwards: row i takes what row i + n held or a row
+// of the step, and the rows it still has to read lie above the ones it has written.
+template <typename T>
+__global__ void conv_state_shift_kernel(const T* __restrict__ rows, int ld, int taps, int C, T* __restrict__ state,
+                                        const int* __restrict__ cu_q, const int* __restrict__ state_slot,
+                                        int n_entries, int n_slots) {
+  ccb::pdl_begin();
+  const int keep = taps - 1;
+  const size_t total = (size_t)n_entries * C;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int e = (int)(i / C), c = (int)(i - (size_t)e * C);
+    const int slot = state_slot[e];
+    if (slot < 0 || slot >= n_slots) continue;
+    const int r0 = cu_q[e], n = cu_q[e + 1] - r0;
+    if (n <= 0) continue;
+    T* st = state + (size_t)slot * keep * C + c;
+    for (int k = 0; k < keep; ++k) {
+      const int src = k + n - keep;   // among the step's rows if >= 0, else the old state's row k + n
+      st[(size_t)k * C] = src >= 0 ? rows[(size_t)(r0 + src) * ld + c] : st[(size_t)(k + n) * C];
+    }
+  }
+}
+
+constexpr int kGateThreads = 256;
+
+// y[t, slice] = v / sqrt(mean(v^2) + eps) * w with v = (o + D_h x) * silu(z); o, x float [T, inner], z in proj.
+template <typename T>
+__global__ void __launch_bounds__(kGateThreads)
+ssm_gate_norm_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __restrict__ xs,
+                     const T* __restrict__ proj, int ld, int oz, const float* __restrict__ Dskip,
+                     const float* __restrict__ w, int P, int inner, int parts, float eps) {
+  ccb::pdl_begin();
+  __shared__ float red[32];
+  const int t = blockIdx.x, part = blockIdx.y;
+  const int width = inner / parts;
+  const int c0 = part * width;
+  const float* orow = o + (size_t)t * inner;
+  const float* xrow = xs + (size_t)t * inner;
+  const T* zrow = proj + (size_t)t * ld + oz;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += kGateThreads) {
+    const int c = c0 + i;
+    const float z = to_f32(zrow[c]);
+    const float v = fmaf(Dskip[c / P], xrow[c], orow[c]) * (z * sigmoid_acc(z));
+    ss += v * v;
+  }
+  ss = block_sum<kGateThreads>(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += kGateThreads) {
+    const int c = c0 + i;
+    const float z = to_f32(zrow[c]);
+    const float v = fmaf(Dskip[c / P], xrow[c], orow[c]) * (z * sigmoid_acc(z));
+    y[(size_t)t * inner + c] = from_f32<T>(v * inv * w[c]);
+  }
+}
+
+}  // namespace
+
+CCB_API int ccb_ssm_prepare(const void* proj, int ld, int ox, int odt, const float* conv_w, const float* conv_b,
+                            int taps, const void* conv_state, const float* A_log, const float* dt_bias,
+                            const int* entry_of_token, const int* cu_q, const int* state_slot, float* xs, float* bs,
+                            float* cs, float* dts, float* as, int rows, int H, int P, int G, int N, int dtype,
+                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (H <= 0 || P <= 0 || G <= 0 || N <= 0 || H % G || taps < 1 || taps > 64) return CCB_REFUSE_SIZE;
+  if (proj == nullptr || conv_w == nullptr || (taps > 1 && conv_state == nullptr)) return CCB_REFUSE_ARG;
+  const size_t total = (size_t)rows * (H * P + 2 * G * N + H);
+  const int threads = 256;
+  const size_t want = (total + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  if (dtype == CCB_F32)
+    ccb_launch(ssm_prepare_kernel<float>, blocks, threads, 0, stream, (const float*)proj, ld, ox, odt, conv_w, conv_b,
+               taps, (const float*)conv_state, A_log, dt_bias, entry_of_token, cu_q, state_slot, xs, bs, cs, dts, as,
+               rows, H, P, G, N);
+  else if (dtype == CCB_BF16)
+    ccb_launch(ssm_prepare_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)proj, ld, ox, odt,
+               conv_w, conv_b, taps, (const __nv_bfloat16*)conv_state, A_log, dt_bias, entry_of_token, cu_q,
+               state_slot, xs, bs, cs, dts, as, rows, H, P, G, N);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}
+
+CCB_API int ccb_conv_state_shift(const void* rows, int ld, int taps, int C, void* state, const int* cu_q,
+                                 const int* state_slot, int n_entries, int n_slots, int dtype, cudaStream_t stream) {
+  if (n_entries <= 0 || taps <= 1) return 0;
+  if (C <= 0) return CCB_REFUSE_SIZE;
+  const size_t total = (size_t)n_entries * C;
+  const int threads = 256;
+  const size_t want = (total + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  if (dtype == CCB_F32)
+    ccb_launch(conv_state_shift_kernel<float>, blocks, threads, 0, stream, (const float*)rows, ld, taps, C,
+               (float*)state, cu_q, state_slot, n_entries, n_slots);
+  else if (dtype == CCB_BF16)
+    ccb_launch(conv_state_shift_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)rows, ld, taps,
+               C, (__nv_bfloat16*)state, cu_q, state_slot, n_entries, n_slots);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}
+
+CCB_API int ccb_ssm_gate_norm(void* y, const float* o, const float* xs, const void* proj, int ld, int oz,
+                              const float* Dskip, const float* w, int rows, int H, int P, int parts, float eps,
+                              int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int inner = H * P;
+  if (H <= 0 || P <= 0 || parts <= 0 || inner % parts) return CCB_REFUSE_SIZE;
+  dim3 grid(rows, parts);
+  if (dtype == CCB_F32)
+    ccb_launch(ssm_gate_norm_kernel<float>, grid, dim3(kGateThreads), 0, stream, (float*)y, o, xs, (const float*)proj,
+               ld, oz, Dskip, w, P, inner, parts, eps);
+  else if (dtype == CCB_BF16)
+    ccb_launch(ssm_gate_norm_kernel<__nv_bfloat16>, grid, dim3(kGateThreads), 0, stream, (__nv_bfloat16*)y, o, xs,
+               (const __nv_bfloat16*)proj, ld, oz, Dskip, w, P, inner, parts, eps);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}

@@ -139,6 +139,13 @@ class Engine:
             elif sn is not None:
                 self._state[i] = torch.zeros((opt.max_requests,) + tuple(sn.shape), dtype=sn.dtype or self.dtype,
                                              device=rt.device)
+        # an embedding that keeps something per request (the previous token, say) gets a state tensor as a mixer does
+        self._embedding_state = None
+        sn = plan.embedding.state_need() if hasattr(plan.embedding, "state_need") else None
+        if sn is not None:
+            self._embedding_state = torch.zeros((opt.max_requests,) + tuple(sn.shape), dtype=sn.dtype or self.dtype,
+                                                device=rt.device)
+            self._state["embedding"] = self._embedding_state
         for i, e in enumerate(plan.order):
             if e.cache_of is not None:
                 if e.cache_of not in self._entry_group:
@@ -420,10 +427,11 @@ class Engine:
 
     def _forward(self, step: StepContext) -> Optional[torch.Tensor]:
         plan = self.plan
+        extra = {"state": self._embedding_state} if self._embedding_state is not None else {}
         if getattr(plan.embedding, "takes_first_norm", False) and plan.order and plan.order[0].enter is None:
-            stream = plan.embedding.forward(step, getattr(plan.layers[plan.order[0].layer], "first_norm", None))
+            stream = plan.embedding.forward(step, getattr(plan.layers[plan.order[0].layer], "first_norm", None), **extra)
         else:
-            stream = plan.embedding.forward(step)
+            stream = plan.embedding.forward(step, **extra)
         first_rows = None
         if any(e.add_embedding or e.enter is not None for e in plan.order):
             # a repeated pass starts from its input plus the embedding's rows: they are kept beside the stream

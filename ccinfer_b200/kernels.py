@@ -159,6 +159,18 @@ _SIGNATURES = {
     "ccb_gemm_tc_pair_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_void_p, c_void_p],
     "ccb_init_random": [c_void_p, c_longlong, c_int, ctypes.c_ulonglong, ctypes.c_ulonglong, c_float, c_int, c_void_p],
+    "ccb_ssm_prepare": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                        c_int, c_int, c_void_p],
+    "ccb_conv_state_shift": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ccb_ssm_gate_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                          c_int, c_float, c_int, c_void_p],
+    "ccb_ssm_recurrence": [c_void_p] * 9 + [c_int] * 5 + [c_void_p],
+    "ccb_attention_talking_fits": [c_int, c_int, c_int],
+    "ccb_attention_talking": [c_void_p] * 10 + [c_int] * 9 + [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "ccb_embed_pair": [c_void_p] * 10 + [c_float] + [c_int] * 9 + [c_void_p, c_int, c_void_p, c_void_p],
+    "ccb_relu_squared": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
+    "ccb_scaled_sum": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_longlong, c_int, c_void_p],
     "ccb_sample_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                         c_int, c_void_p, c_void_p, c_int, c_void_p],
 }
@@ -411,7 +423,8 @@ def qkv_bias_rope_kv_write(qkv, q_out, k_cache, v_cache, positions, slot_map, in
 
 def postnorm_residual(h, delta, w_post, mult: float, eps_post: float, add=None, y=None, w_next=None,
                       eps_next: float = 0.0) -> None:
-    """h += mult * RMSNorm(delta; w_post) [+ add]; with ``w_next``, y = RMSNorm(h; w_next) in the same pass.
+    """h += mult * RMSNorm(delta; w_post) [+ add]; with ``w_next``, y = RMSNorm(h; w_next) in the same pass; with
+    ``y`` alone, y = h in the storage type (for a sublayer that reads the stream itself).
 
     h and add float [T, D]; delta and y in the storage type; the weights float [D].  ``delta`` None: only the
     addition of ``add`` and/or the second norm."""
@@ -576,9 +589,10 @@ def latent_attention(qa, cache, sink, gate, out, cu_q, pos0, entry_of_token, blo
     _cuda(qa, cache, sink, out, cu_q, pos0, entry_of_token, block_table, status)
     T, H, W = qa.shape
     R = out.shape[2]
-    assert out.shape == (T, H, R) and cache.shape[1:] == (page_size, W) and out.dtype == cache.dtype == gate.dtype
-    assert sink.dtype == torch.float32 and sink.numel() == H and gate.stride(1) == 1 and qa.dtype == torch.float32
-    _check(lib().ccb_latent_attention(_p(qa), _p(cache), _p(sink), _p(gate), gate.stride(0), _p(out), _p(cu_q),
+    assert out.shape == (T, H, R) and cache.shape[1:] == (page_size, W) and out.dtype == cache.dtype
+    assert gate is None or (gate.dtype == out.dtype and gate.stride(1) == 1)   # None: no gate
+    assert sink.dtype == torch.float32 and sink.numel() == H and qa.dtype == torch.float32
+    _check(lib().ccb_latent_attention(_p(qa), _p(cache), _p(sink), _p(gate), gate.stride(0) if gate is not None else 0, _p(out), _p(cu_q),
                                       _p(pos0), _p(entry_of_token), _p(block_table), block_table.stride(0), entry0,
                                       n_entries, max_q, H, R, W - R, page_size, cache.shape[0], int(window),
                                       float(scale), _dt(out), _p(status), _stream()), "latent_attention")
@@ -611,13 +625,14 @@ def latent_attention_mma(qa, cache, sink, gate, out, cu_q, pos0, entry_of_token,
     T, H, W = qa.shape
     R = out.shape[2]
     assert out.shape == (T, H, R) and cache.shape[1:] == (page_size, W)
-    assert out.dtype == cache.dtype == gate.dtype == torch.bfloat16
-    assert sink.dtype == torch.float32 and sink.numel() == H and gate.stride(1) == 1 and qa.dtype == torch.float32
+    assert out.dtype == cache.dtype == torch.bfloat16
+    assert gate is None or (gate.dtype == torch.bfloat16 and gate.stride(1) == 1)   # None: no gate
+    assert sink.dtype == torch.float32 and sink.numel() == H and qa.dtype == torch.float32
     if num_splits > 1:
         assert part_acc.dtype == part_ml.dtype == torch.float32 and max_q == 1
         assert part_acc.numel() >= (entry0 + n_entries) * H * num_splits * R
         assert part_ml.numel() >= (entry0 + n_entries) * H * num_splits * 2
-    _check(lib().ccb_latent_attention_mma(_p(qa), _p(cache), _p(sink), _p(gate), gate.stride(0), _p(out), _p(part_acc),
+    _check(lib().ccb_latent_attention_mma(_p(qa), _p(cache), _p(sink), _p(gate), gate.stride(0) if gate is not None else 0, _p(out), _p(part_acc),
                                           _p(part_ml), num_splits, _p(cu_q), _p(pos0), _p(entry_of_token),
                                           _p(block_table), block_table.stride(0), entry0, n_entries, max_q, H, R,
                                           W - R, page_size, cache.shape[0], int(window), float(scale), _p(status),
@@ -794,6 +809,134 @@ def scaled_residual(h, delta, ls, y=None, w_next=None, eps_next: float = 0.0) ->
     assert w_next is None or (y is not None and w_next.dtype == torch.float32 and w_next.numel() == D)
     _check(lib().ccb_scaled_residual(_p(y), _p(h), _p(delta), _p(ls), _p(w_next), float(eps_next), T, D, _dt(delta),
                                      _stream()), "scaled_residual")
+
+
+# ---------------------------------------------------------------------------------------------
+def embed_pair(h, rows, table, pair_table, ids, positions, entry_of_token, cu_q, state_slot, prev_token, scale: float,
+               buckets: int, mul_prev: int, mul_cur: int, n_entries: int, status=None, pending=None) -> None:
+    """h[t, :] = float(table[ids[t], :]) * scale + float(pair_table[row, :]) with row = (previous token * mul_prev +
+    token * mul_cur) mod buckets, or ``buckets`` at position 0; ``pair_table`` None: the first term alone.  The
+    previous token of a portion's first token is ``prev_token[slot]`` (int32 [slots]), which afterwards holds the
+    portion's last token.  ``rows`` (optional): the same values in the storage type."""
+    _cuda(h, rows, table, pair_table, ids, positions, entry_of_token, cu_q, state_slot, prev_token, status, pending)
+    T, D = h.shape
+    assert h.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == D
+    assert rows is None or (rows.shape == (T, D) and rows.dtype == table.dtype)
+    assert pair_table is None or (pair_table.dtype == table.dtype and pair_table.shape == (buckets + 1, D)
+                                  and prev_token is not None and prev_token.dtype == torch.int32)
+    _check(lib().ccb_embed_pair(_p(h), _p(rows), _p(table), _p(pair_table), _p(ids), _p(positions), _p(entry_of_token),
+                                _p(cu_q), _p(state_slot), _p(prev_token), float(scale), int(buckets), int(mul_prev),
+                                int(mul_cur), T, int(n_entries), 0 if prev_token is None else prev_token.numel(), D,
+                                table.shape[0], _dt(table), _p(pending), 0 if pending is None else pending.numel(),
+                                _p(status), _stream()), "embed_pair")
+    if pair_table is not None:
+        counters.own += 1   # the kernel that stores each request's last token
+
+
+def relu_squared(act, x) -> None:
+    """act = relu(x)^2, elementwise."""
+    _cuda(act, x)
+    assert act.shape == x.shape and act.dtype == x.dtype
+    _check(lib().ccb_relu_squared(_p(act), _p(x), x.numel(), _dt(x), _stream()), "relu_squared")
+
+
+def scaled_sum(out, a, b, sa: float, sb: float) -> None:
+    """out = sa * a + sb * b, elementwise (float arithmetic)."""
+    _cuda(out, a, b)
+    assert out.shape == a.shape == b.shape and out.dtype == a.dtype == b.dtype
+    _check(lib().ccb_scaled_sum(_p(out), _p(a), _p(b), float(sa), float(sb), a.numel(), _dt(a), _stream()),
+           "scaled_sum")
+
+
+def ssm_prepare(proj, ox: int, odt: int, conv_w, conv_b, taps: int, conv_state, A_log, dt_bias, entry_of_token, cu_q,
+                state_slot, xs, bs, cs, dts, decay, H: int, P: int, G: int, N: int) -> None:
+    """The inputs of a selective state space recurrence from the input projection's rows ``proj`` [T, >=]: the
+    channels x | B | C (from column ``ox``) pass the convolution ``conv_w`` [taps, channels] (+ ``conv_b``) and silu,
+    rows before the step's first one coming from ``conv_state`` [slots, taps - 1, channels]; dt = softplus(proj[:,
+    odt + h] + dt_bias[h]), decay = exp(-exp(A_log[h]) dt).  Outputs float: xs [T, H, P], bs and cs [T, G, N], dts
+    and decay [T, H]."""
+    _cuda(conv_w, conv_b, conv_state, A_log, dt_bias, entry_of_token, cu_q, state_slot, xs, bs, cs, dts, decay)
+    T = xs.shape[0]
+    C = H * P + 2 * G * N
+    assert proj.stride(1) == 1 and conv_w.dtype == torch.float32 and conv_w.shape == (taps, C)
+    assert conv_state is None or (conv_state.dtype == proj.dtype and tuple(conv_state.shape[1:]) == (max(taps - 1, 1), C))
+    assert xs.dtype == bs.dtype == cs.dtype == dts.dtype == decay.dtype == torch.float32
+    _check(lib().ccb_ssm_prepare(_p(proj), proj.stride(0), int(ox), int(odt), _p(conv_w), _p(conv_b), int(taps),
+                                 _p(conv_state), _p(A_log), _p(dt_bias), _p(entry_of_token), _p(cu_q), _p(state_slot),
+                                 _p(xs), _p(bs), _p(cs), _p(dts), _p(decay), T, H, P, G, N, _dt(proj), _stream()),
+           "ssm_prepare")
+
+
+def conv_state_shift(rows, taps: int, state, cu_q, state_slot, n_entries: int) -> None:
+    """After a convolution over a step's rows: the last taps - 1 of (the request's state rows, then its rows of this
+    step) become the state [slots, taps - 1, C]; ``rows`` [T, C] may be a column slice of wider rows."""
+    _cuda(state, cu_q, state_slot)
+    if taps <= 1:
+        return
+    C = rows.shape[1]
+    assert rows.stride(1) == 1 and state.dtype == rows.dtype and tuple(state.shape[1:]) == (taps - 1, C)
+    _check(lib().ccb_conv_state_shift(_p(rows), rows.stride(0), int(taps), C, _p(state), _p(cu_q), _p(state_slot),
+                                      int(n_entries), state.shape[0], _dt(rows), _stream()), "conv_state_shift")
+
+
+def ssm_recurrence(cs, bs, xs, decay, dts, state, out, cu_q, state_slot, n_entries: int, G: int, H: int, N: int,
+                   P: int) -> None:
+    """S <- decay_t S + B_t (dt_t x_t)^T, out_t = S^T C_t per head over each request's tokens of the step, from and
+    into ``state`` [slots, H, P, N] (float); cs, bs float [T, G, N], xs and out [T, H, P], decay and dts [T, H]."""
+    _cuda(cs, bs, xs, decay, dts, state, out, cu_q, state_slot)
+    assert state.dtype == torch.float32 and state.shape[1:] == (H, P, N) and out.dtype == torch.float32
+    _check(lib().ccb_ssm_recurrence(_p(cs), _p(bs), _p(xs), _p(decay), _p(dts), _p(state), _p(out), _p(cu_q),
+                                    _p(state_slot), n_entries, G, H, N, P, _stream()), "ssm_recurrence")
+
+
+def ssm_gate_norm(y, o, xs, proj, oz: int, skip, w, H: int, P: int, parts: int, eps: float) -> None:
+    """y = RMSNorm in ``parts`` equal slices of ((o + skip[h] * xs) * silu(z)) * w; z = proj[:, oz : oz + H P]."""
+    _cuda(y, o, xs, skip, w)
+    T = y.shape[0]
+    assert proj.stride(1) == 1 and proj.dtype == y.dtype and o.dtype == xs.dtype == torch.float32
+    assert skip.dtype == w.dtype == torch.float32 and skip.numel() == H and w.numel() == H * P
+    _check(lib().ccb_ssm_gate_norm(_p(y), _p(o), _p(xs), _p(proj), proj.stride(0), int(oz), _p(skip), _p(w), T, H, P,
+                                   int(parts), float(eps), _dt(y), _stream()), "ssm_gate_norm")
+
+
+def attention_talking_fits(nq: int, nkv: int, hd: int) -> bool:
+    return bool(lib().ccb_attention_talking_fits(int(nq), int(nkv), int(hd)))
+
+
+TALKING_KEYS = 32   # keys a block takes at a time
+
+
+def attention_talking_splits(n_rows: int, window: int) -> int:
+    """Into how many pieces the key range of a row is cut: enough blocks for two per SM, at most one piece per 32
+    keys of a window, 64 at most.  It depends on the number of rows only, so a step of a given size launches one
+    grid."""
+    most = min(64, -(-window // TALKING_KEYS) + 1) if window else 64
+    return max(1, min(most, split_target_blocks() // max(1, n_rows)))
+
+
+def attention_talking(q, k_cache, v_cache, out, mix, positions, entry_of_token, block_table, window: int,
+                      num_splits: int = 1, part_acc=None, part_ml=None, sink=None, gate=None, status=None) -> None:
+    """Attention whose heads' scores are mixed before the softmax: s_h = sum_g mix[h, g] (q_g . k), over the pages of
+    each row's request; a query at position p sees p - window + 1 .. p (window 0: every j <= p).  q, out
+    [T, nq, hd]; caches [pages, nkv, page_size, hd]; ``mix`` float [nq, nq] (with the score scale in it).  ``sink``
+    float [nq], ``gate`` [T, >= nq] logits (storage type): see AttnExtra.  ``num_splits`` > 1: the key range in
+    pieces, part_acc float [T * splits * nq * hd], part_ml float [T * splits * nq * 2]."""
+    _cuda(q, k_cache, v_cache, out, mix, positions, entry_of_token, block_table, part_acc, part_ml, sink, status)
+    T, nq, hd = q.shape
+    nkv, page_size = k_cache.shape[1], k_cache.shape[2]
+    assert out.shape == q.shape and k_cache.shape == v_cache.shape and k_cache.shape[3] == hd
+    assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype and mix.dtype == torch.float32
+    assert mix.shape == (nq, nq) and (sink is None or (sink.dtype == torch.float32 and sink.numel() == nq))
+    assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1)
+    if num_splits > 1:
+        assert part_acc.numel() >= T * num_splits * nq * hd and part_ml.numel() >= T * num_splits * nq * 2
+    _check(lib().ccb_attention_talking(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_acc), _p(part_ml), _p(mix),
+                                       _p(positions), _p(entry_of_token), _p(block_table), block_table.stride(0), T, nq,
+                                       nkv, hd, page_size, k_cache.shape[0], int(window), int(num_splits), _p(sink),
+                                       _p(gate), gate.stride(0) if gate is not None else 0, _dt(q), _p(status),
+                                       _stream()), "attention_talking")
+    if num_splits > 1:
+        counters.own += 1   # the merge kernel
 
 
 def concat_cast(out, a, b) -> None:

@@ -36,7 +36,11 @@ the softmax denominator (name ``sink``); values mixed with those of the first
 such layer, v <- (1 - lambda) v + lambda v_first, before they are cached
 (``value_mix``); and a gate per head on the result, sigmoid(w_g . x), read from
 the same input as the projections (name ``gate``; its rows ride along in the
-merged projection).
+merged projection); heads that talk to each other before the softmax (names
+``talk`` [heads, heads] and optionally ``temp`` [heads]): head h's score is
+sum_g talk[h, g] * temp[g] * scale * (q_g . k), which one kernel computes for
+all heads of a query together (``csrc/attention_talking.cu``); a position
+encoding with an amplitude on its rotation (``PositionEncoding.amplitude``).
 """
 from __future__ import annotations
 
@@ -93,6 +97,12 @@ class GroupedQueryAttention(Mixer):
             raise Unsupported("biases together with a convolution or value mixing")
         # attention beyond keys and values (every attention kernel takes them)
         self.extras = bool(self.chunk or "sink" in self.names or "gate" in self.names)
+        self.talking = "talk" in self.names
+        if "temp" in self.names and not self.talking:
+            raise Unsupported("a temperature per head comes with the heads' mixing matrix ('talk')")
+        if self.talking and self.chunk:
+            raise Unsupported("heads that talk to each other together with a chunked mask")
+        self.mix = None
         self.float_weights = bool(float_weights)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.qk_dim)
         self.q_width, self.kv_width = self.nq * self.hd, self.nkv * self.hd
@@ -131,6 +141,10 @@ class GroupedQueryAttention(Mixer):
             specs.append(TensorSpec(n["sink"], (self.nq,), role="vector"))
         if "gate" in n:
             specs.append(TensorSpec(n["gate"], (self.nq, D)))
+        if self.talking:
+            specs.append(TensorSpec(n["talk"], (self.nq, self.nq), role="vector"))
+            if "temp" in n:
+                specs.append(TensorSpec(n["temp"], (self.nq,), role="vector", init="one_plus_normal"))
         if "vmix" in n:   # (a layer whose values are the first ones may carry the tensor without using it)
             specs.append(TensorSpec(n["vmix"], (), role="vector"))
         return specs
@@ -213,6 +227,23 @@ class GroupedQueryAttention(Mixer):
             self.q_norm_w = norm_w("q_norm")
             self.k_norm_w = norm_w("k_norm") if self.own_kv else None
             self.norm_eps = self.qk_norm_eps * self.qk_dim / hd
+        amp = self.position.amplitude()
+        if amp is not None:
+            # a factor on cosine and sine is a factor on the rotated coordinate: it rides on the norms' weights
+            if self.qk_norm_eps is None:
+                raise Unsupported("a rotation with an amplitude needs the head norms whose weights carry it")
+            amp = torch.from_numpy(amp).to(rt.device)
+            self.q_norm_w = (self.q_norm_w * amp).contiguous()
+            if self.k_norm_w is not None:
+                self.k_norm_w = (self.k_norm_w * amp).contiguous()
+        if self.talking:
+            if not kernels.attention_talking_fits(self.nq, self.nkv, hd):
+                raise Unsupported(f"{self.nq} heads of {hd} that talk to each other: the kernel's shared memory "
+                                  f"holds every head's query and result rows of a token")
+            mix = fetch(n["talk"]).double()
+            if "temp" in n:
+                mix = mix * fetch(n["temp"]).double()[None, :]
+            self.mix = (mix * self.scale).float().contiguous()
         if self.taps:
             # tap-major for the kernel: [taps, q | k | v channels]
             self.conv_w = torch.cat([qk("q_conv", self.nq), qk("k_conv", self.nkv),
@@ -230,6 +261,18 @@ class GroupedQueryAttention(Mixer):
         a prefill kernel (tcgen05 with 128 query tokens a block, or mma.sync with 64); otherwise every row is
         a single query of the split kernel, which takes all sizes and both types."""
         rt, g = self.rt, cache.group
+        if self.talking:
+            # every head's weights need every head's scores: one kernel owns all heads of a query
+            splits = kernels.attention_talking_splits(T, self.window or 0)
+            acc = ml = None
+            if splits > 1:   # (rows x pieces never exceeds the number of blocks aimed for)
+                most = kernels.split_target_blocks()
+                acc = rt.scratch.get("talk_part_acc", (most * self.nq * self.hd,), torch.float32)
+                ml = rt.scratch.get("talk_part_ml", (most * self.nq * 2,), torch.float32)
+            kernels.attention_talking(q, cache.k, cache.v, o, self.mix, step.positions, step.entry_of_token,
+                                      g.block_table, self.window or 0, splits, acc, ml, sink=self.sink, gate=gate,
+                                      status=rt.status)
+            return
         mma = rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES and not self.float_weights
         extra = {"chunk": self.chunk, "sink": self.sink, "gate": gate} if self.extras else {}
         n_rows = step.n_single if mma else T
@@ -263,7 +306,7 @@ class GroupedQueryAttention(Mixer):
         """A step of single tokens only, on the path of the TMA decode kernel (bfloat16, head size 64 or 128,
         a page size it takes), with few enough rows that every block redoing the queries' norm and rotation
         costs less than a kernel of its own."""
-        return (not self.float_weights and (self.bias is None or self.own_kv)
+        return (not self.float_weights and not self.talking and (self.bias is None or self.own_kv)
                 and self.rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES
                 and kernels.attention_decode_tma_fits(self.hd, g.page_size)
                 and step.n_single == step.n_entries == step.n_tokens
@@ -326,5 +369,5 @@ class GroupedQueryAttention(Mixer):
             else:
                 kernels.qk_norm_rope_kv_write(*args, status=rt.status)
             self._attend(q, o, cache, step, T, gate)
-        out = rt.scratch.get("attn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
+        out = rt.scratch.get(self.out_key, (rt.max_tokens, self.hidden), rt.dtype)[:T]
         return rt.linear(out, o.view(T, self.q_width), self.w_o, sink=step.take_sink())

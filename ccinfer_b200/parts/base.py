@@ -220,6 +220,12 @@ class PositionEncoding(Part):
     def score_bias(self):
         return None
 
+    def amplitude(self):
+        """None, or float32 [head_dim] (the kernels' layout): a factor on both cosine and sine of each coordinate's
+        rotation, i.e. on the rotated coordinate itself.  The attention mixer multiplies it into the weights of its
+        head norms (a rotation is linear) and refuses it where it has none."""
+        return None
+
     def query_temperature(self):
         """(coef, every) if queries are scaled by 1 + coef * ln(floor((pos + 1) / every) + 1), else None."""
         return None
@@ -227,6 +233,7 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     takes_unscaled = False   # True: ``forward`` hands x to ``Runtime.linear`` as it comes (it may be UnscaledRows)
+    out_key = "attn_out"     # the scratch buffer a mixer leaves its result in (two mixers side by side: one each)
 
     def cache_need(self) -> Optional[CacheNeed]:
         return None

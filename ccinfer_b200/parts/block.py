@@ -1,5 +1,7 @@
 """Arrangements of parts in a block.
 
+PostNormBlock: h += post1(Mixer(h)); h += post2(FeedForward(h)): a norm on each sublayer's output only.
+
 PreNormBlock: a = Mixer(norm1(h)); h += a; m = FeedForward(norm2(h)); h += m
 (7QiC/ccInfer: src/model/qwen3/qwen3_model.cpp:141-396).  Each sum is folded
 into the norm that follows it, the last one into the model's final norm.
@@ -237,4 +239,76 @@ class LayerScaleBlock(Block):
             x = self._rows_buffer(after.scratch_key, stream.h.shape[0]) if usable else None
             kernels.postnorm_residual(stream.h, rt.rows(y), self.side.w, 1.0, self.side.eps, y=x,
                                       w_next=after.w if usable else None, eps_next=after.eps if usable else 0.0)
+        stream.ready = (after, x) if (after is not None and x is not None) else None
+
+
+class PostNormBlock(Block):
+    """A norm on each sublayer's OUTPUT only; the sublayers read the stream itself:
+
+        h += post1(Mixer(h));   h += post2(FeedForward(h))
+
+    The feed-forward (with post2) may be absent.  Each sum is one kernel (``kernels.postnorm_residual``) that norms
+    the sublayer's output, adds it and writes what reads the stream next: the stream's own rows in the compute type
+    (for this block's feed-forward, or for a block after it that starts the same way: ``stream.ready``), or the
+    rows of the norm that the block after it starts with.  In the 32-bit path the sublayers get the stream's
+    tensor itself."""
+
+    def __init__(self, dim: int, mixer: Mixer, post1, ffn: Optional[FeedForward] = None, post2=None):
+        from .norm import StreamRows
+        if (ffn is None) != (post2 is None):
+            raise ValueError("a feed-forward comes with its norm, or neither is given")
+        self.dim, self.mixer, self.post1, self.ffn, self.post2 = int(dim), mixer, post1, ffn, post2
+        self.reads = StreamRows(dim)
+        self.rt = None
+
+    def _parts(self):
+        return [p for p in (self.reads, self.mixer, self.post1, self.ffn, self.post2) if p is not None]
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self._parts())
+
+    def tensor_specs(self):
+        return [s for p in self._parts() for s in p.tensor_specs()]
+
+    def bind(self, rt, fetch):
+        self.rt = rt
+        for p in self._parts():
+            p.bind(rt, fetch)
+
+    @property
+    def first_norm(self):
+        return self.reads
+
+    def _sum(self, stream: Residual, delta, post, nxt):
+        """h += post(delta); returns (what ``nxt`` reads, or None): ``nxt`` is a ``StreamRows`` (the stream's own
+        rows) or a norm with a weight and an eps."""
+        from .norm import StreamRows
+        rt = self.rt
+        T = stream.h.shape[0]
+        y = w_next = None
+        eps_next = 0.0
+        if isinstance(nxt, StreamRows):
+            y = None if rt.dtype == torch.float32 else nxt.buffer(T)
+        elif nxt is not None and hasattr(nxt, "w") and hasattr(nxt, "eps"):
+            y = rt.scratch.get(nxt.scratch_key, (rt.max_tokens, nxt.dim), rt.dtype)[:T]
+            w_next, eps_next = nxt.w, nxt.eps
+        kernels.postnorm_residual(stream.h, rt.rows(delta), post.w, 1.0, post.eps, y=y, w_next=w_next,
+                                  eps_next=eps_next)
+        if isinstance(nxt, StreamRows):
+            return stream.h if y is None else y
+        return y
+
+    def forward(self, stream: Residual, step, cache, state) -> None:
+        after = stream.next_norm
+        stream.takes_unscaled = False
+        x = self.reads.fold(stream)
+        step.residual_sink = None
+        a = self.mixer.forward(x, step, cache, state)
+        x = self._sum(stream, a, self.post1, self.reads if self.ffn is not None else after)
+        if self.ffn is not None:
+            m = self.ffn.forward(x, step)
+            x = self._sum(stream, m, self.post2, after)
+        if stream.next_add is not None:
+            x = None   # the engine adds the embedding's rows next: what was written ahead no longer holds
         stream.ready = (after, x) if (after is not None and x is not None) else None

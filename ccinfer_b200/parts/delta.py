@@ -140,5 +140,5 @@ class ChannelGatedDelta(Mixer):
         kernels.delta_recurrence(qn, kn, vv, gg, bb, S, o, step.cu_q, step.state_slot, step.n_entries, G, H, dk, dv)
         y = rt.scratch.get("delta_y", (rt.max_tokens, self.v_width), rt.dtype)[:T]
         kernels.gated_head_rmsnorm(y, o, ag[:, self.oga:], self.norm_w, H, dv, self.eps)
-        out = rt.scratch.get("attn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
+        out = rt.scratch.get(self.out_key, (rt.max_tokens, self.hidden), rt.dtype)[:T]
         return rt.linear(out, y, self.w_o)

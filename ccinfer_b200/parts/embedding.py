@@ -12,30 +12,64 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from .base import Part, Residual, TensorSpec
+from .base import Part, Residual, StateNeed, TensorSpec
 
 
 class TokenEmbedding(Part):
-    def __init__(self, vocab: int, hidden: int, weight_name: str):
+    def __init__(self, vocab: int, hidden: int, weight_name: str, scale: float = 1.0, pair: dict = None):
+        """``scale``: the rows are multiplied by it (in float).  ``pair`` {"name", "buckets", "mul_prev", "mul_cur"}:
+        a second table [buckets + 1, hidden] of which the row (previous token * mul_prev + token * mul_cur) mod
+        buckets is added, the last row for a sequence's first token.  The previous token is state of the request
+        (``state_need``): a portion's first token finds it there."""
         self.vocab, self.hidden, self.weight_name = int(vocab), int(hidden), weight_name
-        self.table = None
+        self.scale = float(scale)
+        self.pair = dict(pair) if pair is not None else None
+        if self.pair is not None:
+            for k in ("buckets", "mul_prev", "mul_cur"):
+                self.pair[k] = int(self.pair[k])
+            if self.pair["buckets"] <= 0 or self.pair["mul_prev"] < 0 or self.pair["mul_cur"] < 0:
+                raise ValueError("a pair table has buckets > 0 and multipliers >= 0")
+        self.table = self.pair_table = None
         self.rt = None
 
     def tensor_specs(self):
-        return [TensorSpec(self.weight_name, (self.vocab, self.hidden))]
+        specs = [TensorSpec(self.weight_name, (self.vocab, self.hidden))]
+        if self.pair is not None:
+            specs.append(TensorSpec(self.pair["name"], (self.pair["buckets"] + 1, self.hidden)))
+        return specs
+
+    def state_need(self):
+        """The previous token of each request, where a pair table is read."""
+        return StateNeed((1,), torch.int32, "prev_token") if self.pair is not None else None
 
     def bind(self, rt, fetch):
         self.rt = rt
         self.table = fetch(self.weight_name)
+        if self.pair is not None:
+            self.pair_table = fetch(self.pair["name"])
 
     takes_first_norm = True
 
-    def forward(self, step, first_norm=None) -> Residual:
+    def forward(self, step, first_norm=None, state=None) -> Residual:
         """``first_norm``: the norm that folds the stream first; where it can, its rows are written by the
-        same kernel as the stream (``stream.ready``)."""
+        same kernel as the stream (``stream.ready``).  ``state``: the tensor of ``state_need``."""
+        from .norm import StreamRows
         rt = self.rt
         h = rt.scratch.get("residual", (rt.max_tokens, self.hidden), torch.float32)[:step.n_tokens]
         pending = getattr(step, "pending_tokens", None)
+        if self.pair is not None or self.scale != 1.0:
+            rows = None
+            if isinstance(first_norm, StreamRows) and rt.dtype != torch.float32:
+                rows = first_norm.buffer(step.n_tokens)
+            p = self.pair or {"buckets": 0, "mul_prev": 0, "mul_cur": 0}
+            kernels.embed_pair(h, rows, self.table, self.pair_table, step.token_ids, step.positions,
+                               step.entry_of_token, step.cu_q, step.state_slot,
+                               state.view(-1) if state is not None else None, self.scale, p["buckets"], p["mul_prev"],
+                               p["mul_cur"], step.n_entries, status=rt.status, pending=pending)
+            stream = Residual(h)
+            if rows is not None:
+                stream.ready = (first_norm, rows)
+            return stream
         y = None
         if first_norm is not None and hasattr(first_norm, "from_embedding"):
             y = first_norm.from_embedding(h, self.table, step.token_ids, pending)

@@ -59,3 +59,31 @@ class ClampedGLU(SwiGLU):
                  shift: float = 1.0):
         super().__init__(hidden, intermediate, names)
         self.activation = ("clamped_glu", float(limit), float(alpha), float(shift))
+
+
+class SquaredReLU(FeedForward):
+    """A feed-forward without a gate: m = (relu(x Wu^T))^2 Wd^T, no biases."""
+
+    def __init__(self, hidden: int, intermediate: int, names: dict):
+        """``names``: tensor names under the keys up, down."""
+        self.hidden, self.inter, self.names = int(hidden), int(intermediate), dict(names)
+        self.w_up = self.w_down = None
+        self.rt = None
+
+    def tensor_specs(self):
+        n = self.names
+        return [TensorSpec(n["up"], (self.inter, self.hidden)), TensorSpec(n["down"], (self.hidden, self.inter))]
+
+    def bind(self, rt, fetch):
+        self.rt = rt
+        self.w_up, self.w_down = fetch(self.names["up"]), fetch(self.names["down"])
+
+    def forward(self, x, step):
+        rt = self.rt
+        x = rt.rows(x)
+        T = x.shape[0]
+        act = rt.scratch.get("ffn_act", (rt.max_tokens, self.inter), rt.dtype)[:T]
+        rt.linear(act, x, self.w_up)
+        kernels.relu_squared(act, act)
+        out = rt.scratch.get("ffn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
+        return rt.linear(out, act, self.w_down)

@@ -94,5 +94,5 @@ class GatedLinearAttention(Mixer):
         kernels.gated_linear_recurrence(qn, kn, vv, gg, state, o, step.cu_q, step.state_slot, step.n_entries, H, dk, dv)
         y = rt.scratch.get("delta_y", (rt.max_tokens, H * dv), rt.dtype)[:T]
         kernels.gated_head_rmsnorm(y, o, proj[:, self.og:], self.norm_w, H, dv, self.eps, silu_gate=True)
-        out = rt.scratch.get("attn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
+        out = rt.scratch.get(self.out_key, (rt.max_tokens, self.hidden), rt.dtype)[:T]
         return rt.linear(out, y, self.w_o)

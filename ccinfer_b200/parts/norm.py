@@ -9,24 +9,29 @@ from .base import Norm, Residual, TensorSpec, UnscaledRows
 
 class RMSNorm(Norm):
     def __init__(self, dim: int, eps: float, weight_name: str, scratch_key: str = "normed", weight_offset: float = 0.0,
-                 weight_scale: float = 1.0):
-        """``weight_offset`` c: the stored weight lies around zero and the norm multiplies by (c + w); the sum is
+                 weight_scale: float = 1.0, scalar: bool = False):
+        """``scalar``: the stored weight is ONE number for all coordinates (a tensor of no axes); it is spread over
+        the ``dim`` places of the kernels' weight vector when it is bound.
+        ``weight_offset`` c: the stored weight lies around zero and the norm multiplies by (c + w); the sum is
         made once, in float, when the weight is bound (exact for a bfloat16 w of ordinary size).
         ``weight_scale`` s: the norm's rows times s (a constant factor on what a product makes of them, a
         model's scale on its logits for instance, costs nothing here)."""
         self.weight_scale = float(weight_scale)
         self.dim, self.eps, self.weight_name, self.scratch_key = int(dim), float(eps), weight_name, scratch_key
         self.weight_offset = float(weight_offset)
+        self.scalar = bool(scalar)
         self.w = None
         self.rt = None
 
     def tensor_specs(self):
-        return [TensorSpec(self.weight_name, (self.dim,), role="vector",
+        return [TensorSpec(self.weight_name, () if self.scalar else (self.dim,), role="vector",
                            init="normal" if self.weight_offset else "one_plus_normal")]
 
     def bind(self, rt, fetch):
         self.rt = rt
         self.w = fetch(self.weight_name)
+        if self.scalar:
+            self.w = self.w.float().reshape(1).expand(self.dim).contiguous()
         if self.weight_offset:
             self.w = (self.w.float() + self.weight_offset).contiguous()
         if self.weight_scale != 1.0:
@@ -82,3 +87,46 @@ class RMSNorm(Norm):
         y = torch.empty_like(x)  # the part alone, outside a step: not a buffer of the pool
         kernels.rmsnorm(y, x, self.w, self.eps)
         return y
+
+
+class StreamRows(Norm):
+    """No norm at all: the rows of the stream itself, in the compute type, for a sublayer that reads the stream as it
+    is.  A block that starts with such a sublayer names one of these as its ``first_norm``, so that whoever writes
+    the stream last (the embedding, the block before) can leave the rows ready in the same pass.  In the 32-bit
+    path the rows ARE the stream."""
+
+    def __init__(self, dim: int, scratch_key: str = "stream_rows"):
+        self.dim, self.scratch_key = int(dim), scratch_key
+        self.rt = None
+        self._ones = None
+
+    def bind(self, rt, fetch):
+        self.rt = rt
+
+    def buffer(self, T: int):
+        rt = self.rt
+        return rt.scratch.get(self.scratch_key, (rt.max_tokens, self.dim), rt.dtype)[:T]
+
+    def fold(self, stream: Residual, rows=None, n_rows=None):
+        rt = self.rt
+        if rows is not None:
+            raise NotImplementedError("the stream's own rows are not gathered by index")
+        ready, stream.ready = stream.ready, None
+        stream.unscaled = None
+        pending, stream.pending = stream.pending, None
+        if pending is None:
+            if rt.dtype == torch.float32:
+                return stream.h
+            if ready is not None and isinstance(ready[0], StreamRows):
+                return ready[1]
+        y = None if rt.dtype == torch.float32 else self.buffer(stream.h.shape[0])
+        if pending is not None:   # a sum that the part before left to whoever reads the stream next
+            if self._ones is None:
+                self._ones = torch.ones(self.dim, dtype=torch.float32, device=rt.device)
+            kernels.scaled_residual(stream.h, rt.rows(pending), self._ones, y=y)
+        else:
+            kernels.postnorm_residual(stream.h, None, None, 0.0, 0.0, y=y)
+        return stream.h if y is None else y
+
+    def apply(self, x):
+        return x

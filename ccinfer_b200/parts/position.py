@@ -40,10 +40,23 @@ class RotaryHalf(PositionEncoding):
     """
 
     def __init__(self, head_dim: int, theta: float, rotary_dim: int = None, interleaved: bool = False,
-                 linear_scaling: float = None, query_temperature=None):
+                 linear_scaling: float = None, query_temperature=None, ramp_scaling: dict = None):
         """``linear_scaling`` s: every frequency is divided by s (positions are stretched by s); the table is
-        then evaluated in float64 and rounded once.  ``query_temperature``: see ``QueryTemperature``."""
+        then evaluated in float64 and rounded once.  ``query_temperature``: see ``QueryTemperature``.
+        ``ramp_scaling`` {"factor", "original", "fast", "slow"}: only the slow pairs are stretched.  With
+        where(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(where(fast)), 0),
+        hi = min(ceil(where(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i
+        turns with f_i / factor * ramp_i + f_i (1 - ramp_i), and cosine and sine are both multiplied by
+        0.1 ln(factor) + 1 (``amplitude``; the attention mixer puts it into the weights of its head norms)."""
         rotary_dim = int(head_dim if rotary_dim is None else rotary_dim)
+        self.ramp_scaling = None
+        if ramp_scaling is not None:
+            if linear_scaling is not None:
+                raise ValueError("linear_scaling or ramp_scaling, not both")
+            self.ramp_scaling = {k: float(ramp_scaling[k]) for k in ("factor", "original", "fast", "slow")}
+            if not (self.ramp_scaling["factor"] > 0 and self.ramp_scaling["original"] > 0
+                    and self.ramp_scaling["fast"] > 0 and self.ramp_scaling["slow"] > 0):
+                raise ValueError("ramp_scaling: factor, original, fast and slow must be > 0")
         if linear_scaling is not None and not (linear_scaling > 0):
             raise ValueError("linear_scaling must be > 0")
         self.linear_scaling = None if linear_scaling is None else float(linear_scaling)
@@ -57,7 +70,9 @@ class RotaryHalf(PositionEncoding):
     def bind(self, rt, fetch):
         self.rt = rt
         table = np.zeros(self.head_dim // 2, dtype=np.float32)
-        if self.linear_scaling is None:
+        if self.ramp_scaling is not None:
+            table[:self.rotary_dim // 2] = self.ramp_frequencies().astype(np.float32)
+        elif self.linear_scaling is None:
             table[:self.rotary_dim // 2] = rotary_inv_freq(self.rotary_dim, self.theta)
         else:
             i = np.arange(self.rotary_dim // 2, dtype=np.float64)
@@ -67,6 +82,33 @@ class RotaryHalf(PositionEncoding):
 
     def rotary_table(self):
         return self.inv_freq
+
+    def ramp_frequencies(self) -> np.ndarray:
+        """float64 [rotary_dim / 2]: the frequencies under ``ramp_scaling``."""
+        import math
+        sc, dims = self.ramp_scaling, self.rotary_dim
+        f = np.power(np.float64(self.theta), -2.0 * np.arange(dims // 2, dtype=np.float64) / dims)
+
+        def where(turns):
+            return dims * math.log(sc["original"] / (2 * math.pi * turns)) / (2 * math.log(self.theta))
+
+        lo = max(math.floor(where(sc["fast"])), 0)
+        hi = min(math.ceil(where(sc["slow"])), dims - 1)
+        ramp = np.clip((np.arange(dims // 2, dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return f / sc["factor"] * ramp + f * (1.0 - ramp)
+
+    def amplitude(self):
+        """None, or float32 [head_dim] in the kernels' layout: the factor on cosine and sine of each coordinate's
+        pair (1 where a coordinate does not turn)."""
+        if self.ramp_scaling is None:
+            return None
+        import math
+        amp = 0.1 * math.log(self.ramp_scaling["factor"]) + 1.0
+        half, rd = self.head_dim // 2, self.rotary_dim // 2
+        v = np.ones(self.head_dim, dtype=np.float32)
+        v[:rd] = amp
+        v[half:half + rd] = amp
+        return v
 
     def query_temperature(self):
         return self._q_temp
