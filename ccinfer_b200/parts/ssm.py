@@ -41,6 +41,7 @@ class SelectiveStateSpace(Mixer):
         self.inner = self.H * self.P
         self.conv_width = self.inner + 2 * self.G * self.N
         self.in_width = 2 * self.inner + 2 * self.G * self.N + self.H
+        self.proj_width = -(-self.in_width // 8) * 8   # rows of the projection's result start on 16 bytes
         self.rt = None
 
     def tensor_specs(self):
@@ -61,6 +62,10 @@ class SelectiveStateSpace(Mixer):
         self.rt = rt
         n = self.names
         self.w_in = fetch(n["in"])
+        if self.proj_width != self.in_width:   # zero rows: columns that nobody reads
+            w = torch.zeros((self.proj_width, self.hidden), dtype=self.w_in.dtype, device=self.w_in.device)
+            w[:self.in_width] = self.w_in
+            self.w_in = w
         self.conv_w = fetch(n["conv"]).float().t().contiguous()      # tap-major
         self.conv_b = fetch(n["conv_bias"]).float().contiguous()
         self.dt_bias = fetch(n["dt_bias"]).float().contiguous()
@@ -75,7 +80,7 @@ class SelectiveStateSpace(Mixer):
         T = x.shape[0]
         H, P, N, G = self.H, self.P, self.N, self.G
         f32 = torch.float32
-        proj = rt.scratch.get("ssm_proj", (rt.max_tokens, self.in_width), rt.dtype)[:T]
+        proj = rt.scratch.get("ssm_proj", (rt.max_tokens, self.proj_width), rt.dtype)[:T]
         rt.linear(proj, x, self.w_in)
         xs = rt.scratch.get("ssm_x", (rt.max_tokens, H, P), f32)[:T]
         bs = rt.scratch.get("ssm_b", (rt.max_tokens, G, N), f32)[:T]

@@ -243,3 +243,150 @@ def generate(cfg, w, prompt, n):
     for _ in range(n):
         toks.append(int(torch.argmax(forward(cfg, w, toks)[-1]).item()))
     return toks[len(prompt):]
+
+
+greedy = generate
+
+
+# ---- configurations of the tests and random weights ----------------------------------------------------------
+def ssm(heads, vdim, state, groups, conv, norm_groups):
+    return ("mamba2", {"heads": heads, "vdim": vdim, "state": state, "groups": groups, "conv": conv,
+                       "norm_groups": norm_groups})
+
+
+def talking(heads, kv_heads, dim, vdim, scale, window=None, rot=None, scaling=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if rot is not None:
+        m["rot"] = {"dims": rot[0], "base": rot[1]}
+        if scaling is not None:
+            m["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    if window is not None:
+        m["mask"] = {"size": window}
+    return m
+
+
+def delta(heads, kv_heads, dim, vdim, conv):
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}
+
+
+def pair(left, right, left_scale, right_scale):
+    return ("parallel", {"left": left, "right": right, "left_scale": left_scale, "right_scale": right_scale})
+
+
+def latent(heads, dim, rot_dim, vdim, rank, scale, base=10000.0, kv_from=None):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank, "scale": scale,
+         "rot": {"dims": rot_dim, "base": base}}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return ("latent_attention", m)
+
+
+def model(vocab, width, eps, layers, scale=1.0, bigram=None):
+    """``layers``: [((type, mixer), ff or None)]; ``bigram``: (buckets, mul_prev, mul_cur)."""
+    e = {"scale": scale}
+    if bigram is not None:
+        e["bigram"] = dict(zip(("buckets", "mul_prev", "mul_cur"), bigram))
+    return {"architecture": "Gevovik", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": e,
+            "layers": [{"type": t, "mixer": m, "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+                       for (t, m), ff in layers]}
+
+
+# name -> (configuration, {layer: (a_rank, g_rank)} of the delta rule's narrow projections, page size)
+CONFIGS = {
+    # a pair first, a window of 24 over pages of 8, half of each head rotated with stretched slow pairs, a layer
+    # without feed-forward, a latent layer that reads another one's rows
+    "A": (model(96, 64, 1e-5, [
+        (pair(talking(4, 2, 16, 8, 0.25, window=24, rot=(8, 10000.0), scaling=(4.0, 16, 4.0, 1.0)),
+              delta(2, 1, 8, 16, 4), 0.7, 1.2), 48),
+        (ssm(4, 8, 16, 2, 3, 2), 40),
+        (latent(2, 8, 4, 8, 16, 0.3), None),
+        (latent(3, 8, 4, 16, 16, 0.25, kv_from=2), 48),
+        (ssm(2, 16, 8, 1, 4, 1), None)], scale=3.0, bigram=(53, 5, 3)), {0: (6, 4)}, 8),
+    # sizes that are multiples of nothing; one head; no pair table; no mask (every earlier key); no scaling; one tap
+    "B": (model(70, 44, 1e-6, [
+        (latent(1, 6, 2, 10, 12, 0.4), 36),
+        (ssm(3, 5, 7, 1, 2, 3), 28),
+        (pair(talking(1, 1, 10, 6, 0.3, rot=(10, 500.0)), delta(1, 1, 6, 10, 1), 1.0, 0.5), None),
+        (ssm(3, 4, 6, 3, 1, 1), 20)], scale=1.0), {2: (3, 5)}, 4),
+    # six heads over two that talk, a window shorter than a page and one of a single token, no rotation in one
+    # pair, latent rows that the tensor-core form takes, two layers reading them
+    "C": (model(128, 96, 1e-5, [
+        (ssm(6, 16, 32, 2, 4, 3), 64),
+        (latent(4, 16, 16, 16, 32, 0.2, base=1000.0), 64),
+        (pair(talking(6, 2, 16, 16, 0.25, window=5, rot=(16, 10000.0), scaling=(2.0, 8, 8.0, 2.0)),
+              delta(4, 2, 16, 8, 2), 0.9, 0.8), 64),
+        (latent(2, 32, 16, 8, 32, 0.15, base=1000.0, kv_from=1), None),
+        (pair(talking(2, 1, 32, 16, 0.2, window=1), delta(2, 2, 8, 8, 3), 1.1, 1.0), 32),
+        (latent(4, 8, 16, 24, 32, 0.2, base=1000.0, kv_from=1), 64)], scale=2.0, bigram=(31, 1, 7)),
+          {2: (8, 8), 4: (2, 16)}, 16),
+}
+
+
+def config(name):
+    cfg, ranks, page = CONFIGS[name]
+    return cfg, dict(ranks), page
+
+
+def tensor_shapes(cfg, ranks):
+    D, V = cfg["width"], cfg["vocab"]
+    s = {"embed": (V, D), "final.norm": (), "head": (V, D)}
+    b = cfg["embedding"].get("bigram")
+    if b is not None:
+        s["bigram"] = (b["buckets"] + 1, D)
+    for i, layer in enumerate(cfg["layers"]):
+        p, m, t = f"l{i}.", layer["mixer"], layer["type"]
+        s[p + "norm1"] = ()
+        q = p + "mix."
+        if t == "mamba2":
+            inner, gn = m["heads"] * m["vdim"], m["groups"] * m["state"]
+            s.update({q + "in": (2 * inner + 2 * gn + m["heads"], D), q + "conv": (inner + 2 * gn, m["conv"]),
+                      q + "conv.b": (inner + 2 * gn,), q + "dt_bias": (m["heads"],), q + "A_log": (m["heads"],),
+                      q + "D": (m["heads"],), q + "norm": (inner,), q + "o": (D, inner)})
+        elif t == "parallel":
+            a, d = m["left"], m["right"]
+            l, r = q + "left.", q + "right."
+            s.update({l + "q": (a["heads"] * a["dim"], D), l + "k": (a["kv_heads"] * a["dim"], D),
+                      l + "v": (a["kv_heads"] * a["vdim"], D), l + "q.norm": (a["dim"],), l + "k.norm": (a["dim"],),
+                      l + "talk": (a["heads"], a["heads"]), l + "temp": (a["heads"],), l + "g": (a["heads"], D),
+                      l + "o": (D, a["heads"] * a["vdim"])})
+            ra, rg = ranks[i]
+            qk, vw = d["kv_heads"] * d["dim"], d["heads"] * d["vdim"]
+            s.update({r + "q": (qk, D), r + "q.conv": (qk, d["conv"]), r + "k": (qk, D), r + "k.conv": (qk, d["conv"]),
+                      r + "v": (vw, D), r + "v.conv": (vw, d["conv"]), r + "b": (d["heads"], D),
+                      r + "A_log": (d["heads"],), r + "norm": (d["vdim"],), r + "a1": (ra, D),
+                      r + "a2": (d["heads"] * d["dim"], ra), r + "dt_bias": (d["heads"] * d["dim"],),
+                      r + "g1": (rg, D), r + "g2": (vw, rg), r + "o": (D, vw)})
+        else:
+            H = m["heads"]
+            s.update({q + "q": (H * (m["dim"] + m["rot_dim"]), D), q + "uk": (H * m["dim"], m["kv_rank"]),
+                      q + "uv": (H * m["vdim"], m["kv_rank"]), q + "sink": (H,), q + "o": (D, H * m["vdim"])})
+            if m.get("kv_from") is None:
+                s.update({q + "dkv": (m["kv_rank"] + m["rot_dim"], D), q + "dkv.norm": (m["kv_rank"],)})
+        if layer["mlp"] is not None:
+            s.update({p + "norm2": (), p + "mlp.up": (layer["mlp"]["ff"], D), p + "mlp.down": (D, layer["mlp"]["ff"])})
+    return s
+
+
+def random_weights(cfg, ranks, seed, sharp=1.0):
+    """Random tensors (values that bfloat16 holds exactly).  Matrices N(0, 1 / fan-in); norm weights around one;
+    ``sharp`` multiplies the attention layers' queries, so that the softmax sits on few keys."""
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in tensor_shapes(cfg, ranks).items():
+        leaf = name.split(".")[-1]
+        if name.endswith(("norm1", "norm2", "final.norm", ".norm", ".D", ".temp")):
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        elif leaf in ("A_log", "dt_bias", "sink", "b") and len(shape) == 1:
+            t = 0.5 * torch.randn(shape, generator=g)
+        elif name.endswith(".conv"):
+            t = torch.randn(shape, generator=g) / math.sqrt(shape[1])
+        elif leaf == "talk":
+            t = torch.eye(shape[0]) + 0.3 * torch.randn(shape, generator=g)
+        elif name in ("embed", "bigram"):
+            t = 0.5 * torch.randn(shape, generator=g)
+        else:
+            t = torch.randn(shape, generator=g) / math.sqrt(shape[-1])
+            if name.endswith((".left.q", "mix.q")) and "right" not in name:
+                t = t * sharp
+        w[name] = t.to(torch.bfloat16).to(torch.float32)
+    return w

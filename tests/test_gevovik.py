@@ -1,0 +1,606 @@
+"""Gevovik in the engine against the plain implementation of ``plain_gevovik``.
+
+Configuration and plan on the CPU; on the GPU the kernels of the design alone, each mixer as the only layer of a
+model, then whole models under every way of cutting the work: whole prompts, token-by-token decoding from the first
+token, portions down to two tokens, mixed batches with pages and state slots that are used again; keys just inside
+and just outside a window, in prompts and in decoding; a far token that decides through a recurrent state; a sink
+that decides; the pair table across portions; long decoding; greedy generation through the Python entry point and
+its scheduler; the programs.
+"""
+import copy
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_gevovik as plain
+
+gpu = pytest.mark.gpu
+
+TOL32 = 3e-5          # relative to the largest logit of the request
+TOL16 = 8e-2
+SHARP = {"float32": 3.0, "bfloat16": 1.5}   # the attention layers' queries times this: the softmax sits on few keys
+
+
+def write_model(path, name=None, cfg=None, ranks=None, seed=0, sharp=1.0, edit=None):
+    from safetensors.torch import save_file
+    if cfg is None:
+        cfg, ranks, _ = plain.config(name)
+    w = plain.random_weights(cfg, ranks, seed, sharp)
+    if edit is not None:
+        edit(w)
+        w = {k: v.to(torch.bfloat16).to(torch.float32) for k, v in w.items()}
+    os.makedirs(path, exist_ok=True)
+    save_file({k: v.to(torch.bfloat16).contiguous() for k, v in w.items()}, os.path.join(path, "model.safetensors"))
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    return cfg, w
+
+
+def engine_of(path, dtype, page, pool, max_requests=4, use_graphs=False, step_tokens=None):
+    from ccinfer_b200.engine.engine import Engine, EngineOptions
+    return Engine.from_model_dir(path, EngineOptions(
+        dtype=dtype, page_size=page, kv_tokens=pool, max_requests=max_requests,
+        max_tokens_per_step=step_tokens or pool, max_context=pool, use_graphs=use_graphs))
+
+
+def compare(rows, ref, dtype, what):
+    """32-bit: every row within TOL32.  bfloat16: a norm on a sublayer's OUTPUT divides by that output's size, so a
+    token whose mixer output nearly cancels has the rounding of that output magnified by the norm (seen with these
+    random weights: one row in 70 moves by a tenth to a third of the largest logit while the median row moves by a
+    hundredth and nine in ten by less than 2.7e-2, the same under every cutting of the work, and the same rows lie
+    within 1e-5 in 32 bits): up to one row in 25 may lie beyond TOL16 while nine in ten lie within half of it."""
+    if dtype == "float32":
+        return helpers.compare(rows, ref, TOL32, what)
+    errs = []
+    for (rid, pos), row in rows.items():
+        assert np.isfinite(row).all(), what
+        errs.append(float(np.abs(row - ref[rid][pos]).max()) / max(1e-6, float(np.abs(ref[rid]).max())))
+    errs = np.sort(np.array(errs))
+    beyond = int((errs > TOL16).sum())
+    assert beyond <= max(1, len(errs) // 25), f"{what}: {beyond} of {len(errs)} rows beyond {TOL16}"
+    p90 = errs[int(0.9 * (len(errs) - 1))]
+    assert p90 <= TOL16 / 2, f"{what}: nine rows in ten should lie within {TOL16 / 2:.1e}, not {p90:.2e}"
+    return float(p90)
+
+
+def requests_of(cfg, lengths, seed):
+    rng = np.random.RandomState(seed)
+    return {f"r{i}": rng.randint(0, cfg["vocab"], size=n).tolist() for i, n in enumerate(lengths)}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU: configuration, plan, the plain implementation against itself
+# ---------------------------------------------------------------------------------------------
+def test_config_is_read_written_and_refused():
+    from ccinfer_b200.config.gevovik import GevovikConfig
+    from ccinfer_b200.config.registry import architecture_of
+    from ccinfer_b200.errors import ModelConfigInvalid
+    cfg, ranks, _ = plain.config("A")
+    assert architecture_of(cfg).name == "Gevovik"
+    c = GevovikConfig.from_json(cfg)
+    assert [l.type for l in c.layers] == ["parallel", "mamba2", "latent_attention", "latent_attention", "mamba2"]
+    assert c.pair.buckets == 53 and c.embed_scale == 3.0 and c.layers[2].mlp is None and c.layers[3].mixer.kv_from == 2
+    left = c.layers[0].mixer.left
+    assert left.window == 24 and left.rot.dims == 8 and left.rot.scaling.factor == 4.0 and left.rot.scaling.slow == 1.0
+    assert c.layers[0].mixer.right.a_rank is None and c.layers[1].mixer.norm_groups == 2
+    full = c.with_shapes(plain.tensor_shapes(cfg, ranks))
+    assert (full.layers[0].mixer.right.a_rank, full.layers[0].mixer.right.g_rank) == (6, 4)
+    assert GevovikConfig.from_json(full.to_json()) == full
+    b = GevovikConfig.from_json(plain.config("B")[0])
+    assert b.pair is None and b.layers[2].mixer.left.window is None and b.layers[2].mixer.left.rot.scaling is None
+    with pytest.raises(ModelConfigInvalid):
+        c.with_shapes({})
+    for damage in (lambda j: j.pop("width"), lambda j: j["norm"].pop("eps"), lambda j: j["embedding"].pop("scale"),
+                   lambda j: j["embedding"]["bigram"].pop("mul_cur"), lambda j: j["layers"][0]["mixer"].pop("left_scale"),
+                   lambda j: j["layers"][0]["mixer"]["left"].pop("scale"),
+                   lambda j: j["layers"][0]["mixer"]["left"]["rot"].update(dims=18),
+                   lambda j: j["layers"][0]["mixer"]["left"]["rot"]["scaling"].pop("fast"),
+                   lambda j: j["layers"][0]["mixer"]["right"].pop("conv"), lambda j: j["layers"][1]["mixer"].pop("state"),
+                   lambda j: j["layers"][1]["mixer"].update(groups=3), lambda j: j["layers"][1].update(type="attention"),
+                   lambda j: j["layers"][2]["mixer"].pop("kv_rank"), lambda j: j["layers"][3]["mixer"].update(kv_from=3),
+                   lambda j: j["layers"][3]["mixer"].update(kv_from=1), lambda j: j["layers"][3]["mixer"].update(kv_rank=8),
+                   lambda j: j["layers"][0]["mlp"].update(kind="moe")):
+        j = copy.deepcopy(cfg)
+        damage(j)
+        with pytest.raises(ModelConfigInvalid):
+            GevovikConfig.from_json(j)
+
+
+def test_plan_names_every_tensor_and_shares_the_latent_rows():
+    from ccinfer_b200.architectures.gevovik import build_plan
+    from ccinfer_b200.config.gevovik import GevovikConfig
+    for name in plain.CONFIGS:
+        cfg, ranks, _ = plain.config(name)
+        shapes = plain.tensor_shapes(cfg, ranks)
+        plan = build_plan(GevovikConfig.from_json(cfg).with_shapes(shapes))
+        plan.validate()
+        assert {s.name: tuple(s.shape) for s in plan.tensor_specs()} == shapes
+        assert [(e.layer, e.cache_of) for e in plan.order] == [(i, l["mixer"].get("kv_from"))
+                                                               for i, l in enumerate(cfg["layers"])]
+
+
+def test_plain_rotation_frequencies():
+    """Without scaling the frequencies are base^(-2i / dims); with it the fast pairs keep theirs, the slow ones are
+    divided by the factor, and both cosine and sine grow by 0.1 ln(factor) + 1."""
+    f, m = plain.rotary_frequencies({"dims": 8, "base": 100.0})
+    assert m == 1.0 and np.allclose(f, [1.0, 100 ** -0.25, 0.1, 100 ** -0.75])
+    f2, m2 = plain.rotary_frequencies({"dims": 8, "base": 100.0,
+                                       "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 0.5}})
+    assert abs(m2 - (0.1 * math.log(4.0) + 1.0)) < 1e-12
+    assert f2[0] == f[0] and abs(f2[-1] - f[-1] / 4.0) < 1e-12 and all(a <= b for a, b in zip(f2, f))
+    from ccinfer_b200.parts.position import RotaryHalf
+    r = RotaryHalf(8, 100.0, ramp_scaling={"factor": 4.0, "original": 64, "fast": 8.0, "slow": 0.5})
+    assert np.allclose(r.ramp_frequencies(), f2, rtol=1e-12) and np.allclose(r.amplitude(), m2)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU: the kernels alone
+# ---------------------------------------------------------------------------------------------
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D", [48, 77, 1000])
+def test_postnorm_residual_writes_the_streams_rows(dtype, D):
+    from ccinfer_b200 import kernels
+    g = torch.Generator().manual_seed(D)
+    T = 5
+    h, w = torch.randn(T, D, generator=g), torch.full((D,), 1.3)
+    delta = (2 * torch.randn(T, D, generator=g)).to(dtype)
+    d64 = delta.double()
+    want = h.double() + d64 / torch.sqrt((d64 * d64).mean(-1, keepdim=True) + 1e-5) * 1.3
+    hd, y = h.cuda(), torch.empty(T, D, dtype=dtype, device="cuda")
+    kernels.postnorm_residual(hd, delta.cuda(), w.cuda(), 1.0, 1e-5, y=y)
+    assert (hd.cpu().double() - want).abs().max() < 1e-5
+    assert (y.cpu().double() - want).abs().max() < (1e-5 if dtype == torch.float32 else 4e-2)
+    y.zero_()
+    kernels.postnorm_residual(hd, None, None, 0.0, 0.0, y=y)       # the rows alone
+    assert (y.cpu().double() - want).abs().max() < (1e-5 if dtype == torch.float32 else 4e-2)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_small_elementwise_kernels(dtype):
+    from ccinfer_b200 import kernels
+    g = torch.Generator().manual_seed(3)
+    for n in (7, 64, 1000):
+        a, b = torch.randn(3, n, generator=g).to(dtype), torch.randn(3, n, generator=g).to(dtype)
+        out = torch.empty(3, n, dtype=dtype, device="cuda")
+        kernels.relu_squared(out, a.cuda())
+        assert torch.equal(out.cpu(), (torch.relu(a.float()) ** 2).to(dtype))
+        kernels.scaled_sum(out, a.cuda(), b.cuda(), 0.7, -1.2)
+        want = 0.7 * a.double() + -1.2 * b.double()
+        assert (out.cpu().double() - want).abs().max() < (1e-6 if dtype == torch.float32 else 2e-2)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pair_embedding_kernel(dtype):
+    """Two requests, one continuing after 5 tokens (its previous token comes from the state), one starting; then
+    the state holds each one's last token."""
+    from ccinfer_b200 import kernels
+    g = torch.Generator().manual_seed(1)
+    V, D, n = 40, 24, 11
+    table, pairs = torch.randn(V, D, generator=g).to(dtype), torch.randn(n + 1, D, generator=g).to(dtype)
+    ids = torch.tensor([7, 3, 39, 0, 12, 5], dtype=torch.int32)
+    pos = torch.tensor([5, 6, 7, 0, 1, 2], dtype=torch.int32)
+    eot = torch.tensor([0, 0, 0, 1, 1, 1], dtype=torch.int32)
+    cu = torch.tensor([0, 3, 6], dtype=torch.int32)
+    slot = torch.tensor([2, 0], dtype=torch.int32)
+    prev = torch.tensor([[33], [0], [21]], dtype=torch.int32).cuda()
+    h = torch.empty(6, D, device="cuda")
+    rows = torch.empty(6, D, dtype=dtype, device="cuda")
+    kernels.embed_pair(h, rows, table.cuda(), pairs.cuda(), ids.cuda(), pos.cuda(), eot.cuda(), cu.cuda(), slot.cuda(),
+                       prev.view(-1), 1.5, n, 4, 9, 2)
+    before = [21, 7, 3, None, 0, 12]
+    for t in range(6):
+        r = n if before[t] is None else (before[t] * 4 + int(ids[t]) * 9) % n
+        want = table[ids[t]].double() * 1.5 + pairs[r].double()
+        assert (h[t].cpu().double() - want).abs().max() < 1e-5, t
+        assert (rows[t].cpu().double() - want).abs().max() < (1e-5 if dtype == torch.float32 else 5e-2)
+    assert prev.view(-1).tolist() == [5, 0, 39]
+
+
+def _paged(x, page, n_pages, perm):
+    """x [T, heads, hd] of ONE request into a cache [n_pages, heads, page, hd] with its pages at ``perm``."""
+    T, Hh, hd = x.shape
+    cache = torch.zeros(n_pages, Hh, page, hd, dtype=x.dtype)
+    for t in range(T):
+        cache[perm[t // page], :, t % page] = x[t]
+    return cache
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(4, 2, 16, 9, 0), (6, 2, 48, 40, 1), (1, 1, 32, 1, 0), (8, 8, 64, 33, 1), (5, 5, 16, 0, 1)])
+def test_talking_attention_kernel(dtype, shape):
+    """The kernel alone over a paged cache whose pages lie in a shuffled order: every query row of a sequence of 70
+    tokens, whole and with the key range in pieces, with and without sink and gate."""
+    from ccinfer_b200 import kernels
+    nq, nkv, hd, window, extras = shape
+    g = torch.Generator().manual_seed(nq * 100 + hd)
+    T, page = 70, 8
+    q = torch.randn(T, nq, hd, generator=g).to(dtype)
+    k = torch.randn(T, nkv, hd, generator=g).to(dtype)
+    v = torch.randn(T, nkv, hd, generator=g).to(dtype)
+    mix = (torch.eye(nq) + 0.4 * torch.randn(nq, nq, generator=g)) * (1.5 / math.sqrt(hd))
+    sink = torch.randn(nq, generator=g) if extras else None
+    gate = torch.randn(T, nq + 3, generator=g).to(dtype) if extras else None
+    n_pages = 12
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    rep = nq // nkv
+    s = torch.einsum("ihd,jhd->hij", q.double(), k.double().repeat_interleave(rep, 1))
+    s = torch.einsum("hg,gij->hij", mix.double(), s)
+    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    seen = (j <= i) & ((i - j < window) if window else True)
+    s = s.masked_fill(~seen[None], float("-inf"))
+    if sink is not None:
+        s = torch.cat([s, sink.double()[:, None, None].expand(nq, T, 1)], -1)
+    a = torch.softmax(s, -1)[..., :T]
+    want = torch.einsum("hij,jhd->ihd", a, v.double().repeat_interleave(rep, 1))
+    if gate is not None:
+        want = want * torch.sigmoid(gate.double()[:, :nq])[:, :, None]
+    bt = torch.full((1, 16), -1, dtype=torch.int32)
+    bt[0, :len(perm)] = torch.tensor(perm, dtype=torch.int32)
+    args = (q.cuda(), _paged(k, page, n_pages, perm).cuda(), _paged(v, page, n_pages, perm).cuda())
+    pos = torch.arange(T, dtype=torch.int32).cuda()
+    eot = torch.zeros(T, dtype=torch.int32).cuda()
+    for splits in (1, 3):
+        out = torch.full((T, nq, hd), float("nan"), dtype=dtype, device="cuda")
+        acc = torch.empty(T * splits * nq * hd, device="cuda") if splits > 1 else None
+        ml = torch.empty(T * splits * nq * 2, device="cuda") if splits > 1 else None
+        kernels.attention_talking(*args, out, mix.cuda(), pos, eot, bt.cuda(), window, splits, acc, ml,
+                                  sink=None if sink is None else sink.cuda(), gate=None if gate is None else gate.cuda())
+        err = (out.cpu().double() - want).abs().max()
+        assert err < (2e-5 if dtype == torch.float32 else 3e-2), (shape, splits, float(err))
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU: each mixer as the only layer of a model
+# ---------------------------------------------------------------------------------------------
+ALONE = {
+    "state space, groups": plain.ssm(4, 8, 16, 2, 4, 2),
+    "state space, one tap, odd sizes": plain.ssm(3, 5, 7, 3, 1, 1),
+    "state space, a state of 200": plain.ssm(2, 8, 200, 1, 5, 4),
+    "talking attention beside the delta rule": plain.pair(
+        plain.talking(4, 2, 16, 16, 0.25, window=20, rot=(16, 10000.0), scaling=(8.0, 8, 2.0, 0.5)),
+        plain.delta(2, 2, 8, 8, 3), 0.6, 1.4),
+    "unequal head sizes, part of the head rotated, no mask": plain.pair(
+        plain.talking(3, 1, 20, 12, 0.3, rot=(6, 50.0)), plain.delta(1, 1, 6, 10, 2), 1.0, 1.0),
+    "latent attention": plain.latent(3, 8, 4, 8, 16, 0.3),
+    "latent attention, tensor-core sizes": plain.latent(4, 16, 16, 32, 64, 0.2),
+}
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("what", list(ALONE))
+def test_each_mixer_alone(tmp_path, what, dtype):
+    cfg = plain.model(64, 48, 1e-5, [(ALONE[what], None)], scale=2.0, bigram=(17, 3, 5))
+    d = str(tmp_path / "alone")
+    cfg, w = write_model(d, cfg=cfg, ranks={0: (4, 6)}, seed=len(what), sharp=SHARP[dtype])
+    reqs = requests_of(cfg, [1, 2, 19, 20, 21, 22, 47, 90], 3)
+    ref = {rid: plain.forward(cfg, w, t).numpy() for rid, t in reqs.items()}
+    for steps in (helpers.trace_whole(reqs), helpers.trace_prefill_then_decode(reqs, tail=25),
+                  helpers.trace_mixed(reqs, max_live=3, seed=2, portion_choices=(2, 3, 33, 9, 70))):
+        eng = engine_of(d, dtype, 8, helpers.max_live_tokens(steps, round_to=64), max_requests=3)
+        rows = helpers.replay(eng, steps)
+        compare(rows, ref, dtype, f"{what} {dtype}")
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU: whole models under every cutting
+# ---------------------------------------------------------------------------------------------
+# prompt lengths just below, at and just above the windows (24; 5, 1) and the pages' borders (8; 4; 16)
+LENGTHS = {"A": [1, 2, 8, 9, 23, 24, 25, 26, 60, 97], "B": [1, 3, 4, 5, 8, 9, 31, 32, 75],
+           "C": [2, 4, 5, 6, 7, 16, 17, 33, 70, 130]}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for name in plain.CONFIGS:
+        for dtype, sharp in SHARP.items():
+            d = str(tmp_path_factory.mktemp("gev" + name))
+            cfg, w = write_model(d, name, seed=ord(name), sharp=sharp)
+            reqs = requests_of(cfg, LENGTHS[name], 2)
+            ref = {rid: plain.forward(cfg, w, t).numpy() for rid, t in reqs.items()}
+            out[name, dtype] = (d, cfg, w, reqs, ref, plain.CONFIGS[name][2])
+    return out
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(plain.CONFIGS))
+@pytest.mark.parametrize("mode", ["whole", "decode from the first token", "decode40", "portions", "mixed"])
+def test_replay_matches_plain(models, name, dtype, mode):
+    d, cfg, w, reqs, ref, page = models[name, dtype]
+    if mode == "whole":
+        steps = helpers.trace_whole(reqs)
+    elif mode == "decode from the first token":
+        steps = helpers.trace_prefill_then_decode(reqs, tail=10 ** 6)
+    elif mode == "decode40":
+        steps = helpers.trace_prefill_then_decode(reqs, tail=40)
+    elif mode == "portions":
+        steps = helpers.trace_portions(reqs)
+    else:
+        steps = helpers.trace_mixed(reqs, max_live=4, seed=5)
+    pool = helpers.max_live_tokens(steps, round_to=max(64, page))
+    eng = engine_of(d, dtype, page, pool, max_requests=4)
+    rows = helpers.replay(eng, steps)
+    assert len(rows) == sum(len(t) for t in reqs.values())
+    worst = compare(rows, ref, dtype, f"{name} {dtype} {mode}")
+    print(f"[worst] {name}, {dtype}, {mode}: {worst:.3e}")
+    eng.cache.check_consistency()
+    assert all(p.used_pages == 0 for p in eng.cache.pools)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_portions_and_graphs(models, dtype):
+    """Portions of more than 64 tokens after a cached prefix beside decode steps replayed from CUDA graphs."""
+    d, cfg, w, reqs, ref, page = models["C", dtype]
+    steps = helpers.trace_mixed(reqs, max_live=3, seed=13, prefill_frac=0.8, portion_choices=(70, 130, 65, 2, 100))
+    pool = helpers.max_live_tokens(steps, round_to=64)
+    eng = engine_of(d, dtype, page, pool, max_requests=4, use_graphs=True)
+    rows = helpers.replay(eng, steps)
+    worst = compare(rows, ref, dtype, f"C {dtype} long portions, graphs")
+    print(f"[worst] C, {dtype}, long portions, graphs: {worst:.3e}")
+    assert eng.graph_replays > 0
+
+
+@gpu
+def test_a_slot_that_is_used_again_starts_from_zero(models):
+    """Two state slots, five requests one after another and in pairs: every later request gets a slot whose
+    recurrent states, convolution rows and previous token an earlier one left behind."""
+    d, cfg, w, reqs, ref, page = models["A", "float32"]
+    eng = engine_of(d, "float32", page, 256, max_requests=2)
+    ids = list(reqs)[4:9]
+    for group in ([ids[0]], [ids[1], ids[2]], [ids[3], ids[4]]):
+        steps = helpers.trace_mixed({r: reqs[r] for r in group}, max_live=2, seed=1)
+        rows = helpers.replay(eng, steps)
+        helpers.compare(rows, ref, TOL32, "slots used again")
+    assert eng.cache.slots.free_slots == 2
+
+
+def _one_layer(mix, ff=None, **kw):
+    return plain.model(64, 32, 1e-5, [(mix, ff)], **kw)
+
+
+@gpu
+def test_a_key_at_the_windows_edge_decides(tmp_path):
+    """One pair whose delta-rule half is switched off and whose attention has a window of 20.  Queries and keys read
+    the first half of the stream, values the second; tokens 0 and 1 share their first half and have opposite second
+    halves, so the query of token 1 matches the key of token 0 as well as its own and hardly any other.  Token 1
+    ends the sequence; token 0 stands 19 places back (the last key the window keeps) or 20 places back (the first
+    it drops).  In a prompt, in portions that end at the edge, and decoded."""
+    cfg = _one_layer(plain.pair(plain.talking(2, 1, 16, 16, 0.25, window=20), plain.delta(1, 1, 8, 8, 2), 1.0, 0.0))
+    d = str(tmp_path / "edge")
+
+    def edit(w):
+        p = "l0.mix.left."
+        w[p + "k"][:, 16:] = 0
+        w[p + "v"][:, :16] = 0
+        w[p + "q"] = torch.cat([w[p + "k"], w[p + "k"]], 0) * 6.0
+        w[p + "q.norm"] = torch.ones_like(w[p + "q.norm"]) * 4.0
+        w[p + "k.norm"] = torch.ones_like(w[p + "k.norm"]) * 4.0
+        w[p + "talk"] = torch.tensor([[1.0, 0.25], [-0.25, 1.0]])
+        w[p + "g"] = torch.zeros_like(w[p + "g"])
+        w["embed"][2:, :16] *= 0.2
+        w["embed"][1, :16] = w["embed"][0, :16]
+        w["embed"][1, 16:] = -w["embed"][0, 16:]
+
+    cfg, w = write_model(d, cfg=cfg, ranks={0: (4, 4)}, seed=11, edit=edit)
+    rng = np.random.RandomState(0)
+    for back in (19, 20):
+        toks = rng.randint(2, 64, size=90).tolist()
+        toks[-1 - back], toks[-1] = 0, 1
+        ref = plain.forward(cfg, w, toks).numpy()
+        other = list(toks)
+        other[-1 - back] = 2
+        moved = np.abs(ref[-1] - plain.forward(cfg, w, other).numpy()[-1]).max() / np.abs(ref[-1]).max()
+        assert (moved > 0.1) == (back == 19), (back, moved)    # inside the window the key decides, outside it is gone
+        for dtype in ("float32", "bfloat16"):
+            eng = engine_of(d, dtype, 8, 128)
+            reqs = {"a": toks}
+            for steps in (helpers.trace_whole(reqs), helpers.trace_prefill_then_decode(reqs, tail=30),
+                          helpers.trace_portions(reqs, sizes=(90 - back - 1, 2, back - 2, 1)),
+                          helpers.trace_portions(reqs, sizes=(90 - back, back - 1, 1))):
+                rows = helpers.replay(eng, steps)
+                compare(rows, {"a": ref}, dtype, f"key {back} back")
+
+
+@gpu
+def test_a_sink_decides(tmp_path):
+    """Sinks far above every score, in a latent layer with rows of its own and in one that reads them: most of each
+    softmax's weight goes to the term that has no value."""
+    cfg = plain.model(64, 32, 1e-5, [(plain.latent(3, 8, 4, 8, 16, 0.3), None),
+                                     (plain.latent(2, 8, 4, 8, 16, 0.3, kv_from=0), None)])
+    d = str(tmp_path / "sink")
+    sinks = {"l0.mix.sink": torch.tensor([4.0, 6.0, -1.0]), "l1.mix.sink": torch.tensor([5.0, 3.0])}
+    cfg, w = write_model(d, cfg=cfg, ranks={}, seed=12, edit=lambda w: w.update(sinks))
+    toks = np.random.RandomState(1).randint(0, 64, size=40).tolist()
+    ref = plain.forward(cfg, w, toks).numpy()
+    low = dict(w, **{k: torch.full_like(v, -30.0) for k, v in sinks.items()})
+    assert np.abs(plain.forward(cfg, low, toks).numpy() - ref).max() > 0.2 * np.abs(ref).max()
+    for dtype in ("float32", "bfloat16"):
+        eng = engine_of(d, dtype, 4, 64)
+        for steps in (helpers.trace_whole({"a": toks}), helpers.trace_prefill_then_decode({"a": toks}, tail=20)):
+            rows = helpers.replay(eng, steps)
+            compare(rows, {"a": ref}, dtype, "sink")
+
+
+@gpu
+def test_a_far_token_decides_through_the_state(tmp_path):
+    """One state space layer whose decay is nearly one.  B and C read the first half of the stream, x the second;
+    tokens 0 and 1 share their first half.  Token 0 stands at ONE far place among 400 and token 1 at the end: what
+    the state kept of the far token decides the last logits.  The far place is the first token, around a page
+    border and the middle; the prompt is cut so that the state crosses steps."""
+    cfg = _one_layer(plain.ssm(2, 8, 16, 1, 2, 1))
+    d = str(tmp_path / "far")
+
+    def edit(w):
+        p = "l0.mix."
+        inner, gn = 16, 16
+        win = w[p + "in"]
+        win[inner:2 * inner, :16] = 0                 # x reads the second half
+        win[2 * inner:2 * inner + gn, 16:] = 0        # B reads the first half
+        win[2 * inner + gn:2 * inner + 2 * gn] = win[2 * inner:2 * inner + gn] * 2.0   # C = 2 B
+        win[2 * inner + 2 * gn:] = 0                  # the step size comes from its bias alone
+        w[p + "conv"] = torch.zeros_like(w[p + "conv"])
+        w[p + "conv"][:, -1] = 3.0                    # the convolution passes the current token only
+        w[p + "conv.b"] = torch.zeros_like(w[p + "conv.b"])
+        w[p + "A_log"] = torch.full_like(w[p + "A_log"], -7.0)
+        w[p + "dt_bias"] = torch.zeros_like(w[p + "dt_bias"])
+        w[p + "D"] = torch.zeros_like(w[p + "D"])
+        w["embed"][2:, :16] *= 0.05
+        w["embed"][1, :16] = w["embed"][0, :16]
+
+    cfg, w = write_model(d, cfg=cfg, ranks={}, seed=8, edit=edit)
+    rng = np.random.RandomState(0)
+    for far_at in (0, 7, 8, 200):
+        toks = rng.randint(2, 64, size=400).tolist()
+        toks[far_at], toks[-1] = 0, 1
+        ref = plain.forward(cfg, w, toks).numpy()
+        without = plain.forward(cfg, w, toks[:far_at] + [2] + toks[far_at + 1:]).numpy()
+        assert np.abs(ref[-1] - without[-1]).max() > 0.15 * np.abs(ref[-1]).max()
+        for dtype in ("float32", "bfloat16"):
+            eng = engine_of(d, dtype, 8, 448)
+            reqs = {"a": toks}
+            for steps in (helpers.trace_whole(reqs), helpers.trace_prefill_then_decode(reqs, tail=3),
+                          helpers.trace_portions(reqs, sizes=(150, 2, 100, 147, 1))):
+                rows = helpers.replay(eng, steps)
+                compare(rows, {"a": ref}, dtype, f"far token at {far_at}")
+
+
+@gpu
+def test_the_pair_table_decides_across_portions(tmp_path):
+    """The token's own row is nearly switched off, so the stream starts from the row that (previous token, token)
+    chooses: a wrong previous token at the start of a portion, or the wrong row for a sequence's first token,
+    changes every logit of that position."""
+    cfg = _one_layer(plain.ssm(2, 8, 8, 1, 2, 1), ff=24, scale=0.01, bigram=(29, 7, 11))
+    d = str(tmp_path / "pairs")
+    cfg, w = write_model(d, cfg=cfg, ranks={}, seed=5, edit=lambda w: w.update(bigram=w["bigram"] * 4.0))
+    reqs = requests_of(cfg, [1, 2, 9, 30], 7)
+    ref = {rid: plain.forward(cfg, w, t).numpy() for rid, t in reqs.items()}
+    for dtype in ("float32", "bfloat16"):
+        for steps in (helpers.trace_whole(reqs), helpers.trace_portions(reqs, sizes=(1, 2, 3, 1, 5)),
+                      helpers.trace_mixed(reqs, max_live=2, seed=3, portion_choices=(2, 3))):
+            eng = engine_of(d, dtype, 4, 128, max_requests=2)
+            rows = helpers.replay(eng, steps)
+            compare(rows, ref, dtype, "pair table")
+
+
+@gpu
+def test_long_decoding(models):
+    """260 tokens one by one: the window passes over decoded tokens many times, its pages are given back."""
+    rng = np.random.RandomState(9)
+    for dtype in ("float32", "bfloat16"):
+        d, cfg, w, reqs, ref, page = models["A", dtype]
+        toks = rng.randint(0, cfg["vocab"], size=260).tolist()
+        want = plain.forward(cfg, w, toks).numpy()
+        eng = engine_of(d, dtype, page, 320, use_graphs=(dtype == "bfloat16"))
+        rows = helpers.replay(eng, helpers.trace_prefill_then_decode({"a": toks}, tail=10 ** 6))
+        worst = compare(rows, {"a": want}, dtype, f"long decoding {dtype}")
+        print(f"[worst] long decoding, {dtype}: {worst:.3e}")
+        assert all(p.used_pages <= 320 // page for p in eng.cache.pools)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_entry_point(models, dtype):
+    """Prompts of unequal length in portions of 7 through ``LLM.generate`` and its scheduler."""
+    from ccinfer_b200 import LLM, SamplingParams
+    d, cfg, w, reqs, ref, page = models["B", dtype]
+    rng = np.random.RandomState(4)
+    prompts = [rng.randint(0, cfg["vocab"], size=n).tolist() for n in (1, 9, 20, 33)]
+    llm = LLM(d, dtype=dtype, page_size=page, kv_tokens=512, prefill_chunk_size=7, max_requests=4,
+              max_tokens_per_step=64)
+    got = llm.generate(prompts, SamplingParams(max_tokens=10))
+    if dtype == "float32":
+        assert got == [plain.greedy(cfg, w, p, 10) for p in prompts]
+    else:   # rounding may flip an argmax between two close logits: every token must be (nearly) the best one
+        for p, new in zip(prompts, got):
+            toks = list(p)
+            for t in new:
+                row = plain.forward(cfg, w, toks)[-1]
+                assert row[t] >= row.max() - 0.05 * row.abs().max()
+                toks.append(t)
+    assert all(pool.used_pages == 0 for pool in llm.engine.cache.pools)
+
+
+@gpu
+def test_the_programs_as_a_user_calls_them(models, tmp_path):
+    """bin/ccinfer: greedy tokens of a model folder; a random model written from a configuration generates the
+    same tokens as the same configuration drawn on the device; bin/trace_run: a mixed trace over four request
+    slots, its files against the plain logits."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    d, cfg, w, reqs, ref, page = models["A", "float32"]
+    exe = [sys.executable, os.path.join(root, "bin", "ccinfer")]
+    prompt = list(reqs.values())[5]
+    r = subprocess.run(exe + ["--model-path", d, "--dtype", "float32", "--page-size", str(page), "--kv-tokens", "256",
+                              "--max-tokens", "6", "--prompt-ids", ",".join(map(str, prompt))],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[0])["token_ids"] == plain.greedy(cfg, w, prompt, 6)
+
+    from ccinfer_b200.config.gevovik import GevovikConfig
+    full = GevovikConfig.from_json(cfg).with_shapes(plain.tensor_shapes(cfg, plain.CONFIGS["A"][1])).to_json()
+    cj = str(tmp_path / "config.json")
+    with open(cj, "w") as f:
+        json.dump(full, f)
+    common = ["--dtype", "float32", "--kv-tokens", "256", "--max-tokens", "5", "--random-prompts", "9,4",
+              "--weights-seed", "5", "--weights-std", "0.3"]
+    a = subprocess.run(exe + ["--random-config", cj] + common, capture_output=True, text=True, timeout=600)
+    assert a.returncode == 0, a.stderr[-2000:]
+    made = str(tmp_path / "made")
+    wr = subprocess.run(exe + ["--model-path", made, "--write-random-model", cj, "--weights-seed", "5",
+                               "--weights-std", "0.3"], capture_output=True, text=True, timeout=600)
+    assert wr.returncode == 0, wr.stderr[-2000:]
+    b = subprocess.run(exe + ["--model-path", made] + common, capture_output=True, text=True, timeout=600)
+    assert b.returncode == 0, b.stderr[-2000:]
+    assert a.stdout == b.stdout and len(a.stdout.strip().splitlines()) == 2
+
+    steps = helpers.trace_mixed(reqs, max_live=4, seed=3)
+    pool = helpers.max_live_tokens(steps)
+    out_dir = tmp_path / "out"
+    lines = "".join(json.dumps({"step": i, **st}) + "\n" for i, st in enumerate(steps))
+    t = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", "float32", "--out",
+                        str(out_dir), "--max-tokens", str(pool)], input=lines, capture_output=True, text=True,
+                       timeout=600)
+    assert t.returncode == 0, t.stderr[-2000:]
+    assert t.stdout.split() == [x for i in range(len(steps)) for x in ("done", str(i))]
+    rows, seen = {}, {rid: 0 for rid in reqs}
+    for i, st in enumerate(steps):
+        n_want = sum(len(e["want"]) for e in st["entries"])
+        arr = np.fromfile(out_dir / f"{i}.f32", dtype="<f4").reshape(n_want, cfg["vocab"])
+        at = 0
+        for e in st["entries"]:
+            for wnt in e["want"]:
+                rows[(e["id"], seen[e["id"]] + wnt)] = arr[at]
+                at += 1
+            seen[e["id"]] += len(e["tokens"])
+    assert len(rows) == sum(len(x) for x in reqs.values())
+    helpers.compare(rows, ref, TOL32, "trace_run")
+
+
+@gpu
+def test_a_preempted_request_starts_its_state_again(models):
+    """So few pages that a request is preempted and computed again (its slot is closed and opened: the recurrent
+    states and the previous token start again, the pages are taken anew): the greedy tokens are those of a calm
+    run."""
+    from ccinfer_b200 import LLM, SamplingParams
+    d, cfg, w, reqs, ref, page = models["A", "float32"]
+    rng = np.random.RandomState(6)
+    prompts = [rng.randint(0, cfg["vocab"], size=n).tolist() for n in (20, 26, 17)]
+    llm = LLM(d, dtype="float32", page_size=page, kv_tokens=8 * page, prefill_chunk_size=16, max_requests=4,
+              max_tokens_per_step=64)
+    got = llm.generate(prompts, [SamplingParams(max_tokens=n) for n in (24, 20, 28)])
+    assert llm.scheduler.preemptions > 0
+    assert got == [plain.greedy(cfg, w, p, n) for p, n in zip(prompts, (24, 20, 28))]
+    llm.engine.cache.check_consistency()
