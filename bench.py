@@ -35,10 +35,10 @@ runs one of the two other workloads of the reference's benchmark record through 
 continuous batch at the Qwen3-14B shape; four 16,384-token prompts at the Qwen3-32B shape) and prints a
 line of its own: output tokens a second, the distribution of the step calls, the pages' high water.
 
-    python bench.py --design tugelorn|dufizen|burolorn [--design-sizes mid,8b] [--layers L] [--design-profile]
+    python bench.py --design tugelorn|dufizen|burolorn|gevovik [--design-sizes mid,8b] [--layers L] [--design-profile]
 
 measures another design of the package beside its closest model (Tugelorn beside Qwen3, Dufizen beside
-Tugelorn, Burolorn beside Qwen3) at equal layer sizes (same width, heads, head size,
+Tugelorn, Burolorn beside Qwen3, Gevovik beside Tugelorn) at equal layer sizes (same width, heads, head size,
 intermediate size, vocabulary and number of layers; random weights): one prompt of 2,048 and of 8,192 tokens
 in steps of 2,048 (tokens a second) and decode steps of 1 and 8 requests after 2,048-token prompts, replayed
 from CUDA graphs (tokens a second), one JSON line per size.  With --design-profile it only runs a prompt and a
@@ -334,6 +334,43 @@ def burolorn_config(size: str, layers: int):
     return BurolornConfig.from_json(j)
 
 
+def gevovik_config(size: str, layers: int):
+    """Layers in turn: a state space layer (2 D inner channels in heads of 64, a state of 128, 8 groups, four taps),
+    a pair of attention over a window of 1,024 whose heads talk before the softmax (head norms, stretched rotation,
+    gate) beside a gated delta rule of half as many heads, and latent attention over every earlier token (latent
+    size 512, 64 rotated coordinates, a sink), every second one of which reads the rows of the first; each with a
+    squared-ReLU feed-forward of F; norms on the sublayers' outputs; an embedding with a pair table."""
+    from ccinfer_b200.config.gevovik import GevovikConfig
+    D, H, G, hd, F, V = DESIGN_SIZES[size]
+    ssm = {"type": "mamba2", "mixer": {"heads": 2 * D // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4,
+                                       "norm_groups": 8}}
+    pair = {"type": "parallel", "mixer": {
+        "left": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": 1024},
+                 "rot": {"dims": hd, "base": 1000000.0,
+                         "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+        "right": {"heads": H // 2, "kv_heads": H // 2, "dim": hd, "vdim": hd, "conv": 4, "a_rank": hd, "g_rank": hd},
+        "left_scale": 0.8, "right_scale": 0.9}}
+    latent = {"heads": H, "dim": hd - 64, "rot_dim": 64, "vdim": hd, "kv_rank": 512, "scale": hd ** -0.5,
+              "rot": {"dims": 64, "base": 1000000.0}}
+    mlp = {"kind": "dense", "ff": F}
+    out, first_latent = [], None
+    for i in range(layers):
+        if i % 3 == 0:
+            out.append(dict(ssm, mlp=mlp))
+        elif i % 3 == 1:
+            out.append(dict(pair, mlp=mlp))
+        else:
+            m = dict(latent)
+            if first_latent is None:
+                first_latent = i
+            elif (i // 3) % 2 == 1:
+                m["kv_from"] = first_latent
+            out.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+    j = {"architecture": "Gevovik", "vocab": V, "width": D, "norm": {"eps": 1e-5},
+         "embedding": {"scale": D ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": out}
+    return GevovikConfig.from_json(j)
+
+
 def run_design(args) -> int:
     import numpy as np
     import torch
@@ -343,7 +380,7 @@ def run_design(args) -> int:
 
     # design -> (its configuration at a size, the closest model it is measured beside)
     designs = {"tugelorn": (tugelorn_config, "qwen3"), "dufizen": (dufizen_config, "tugelorn"),
-               "burolorn": (burolorn_config, "qwen3")}
+               "burolorn": (burolorn_config, "qwen3"), "gevovik": (gevovik_config, "tugelorn")}
     if args.design not in designs:
         print(json.dumps({"error": f"unknown design {args.design!r}"}))
         return 2
@@ -461,7 +498,7 @@ def main() -> int:
     ap.add_argument("--shape", default="8b", choices=["8b", "14b", "32b"], help="layer shape of --profile-steps")
     ap.add_argument("--workload", default="decode", choices=["decode", "mix14b", "long32b"],
                     help="decode (the default line) or one of the two other workloads of the benchmark record")
-    ap.add_argument("--design", default=None, help="tugelorn (beside Qwen3), dufizen (beside Tugelorn) or burolorn (beside Qwen3): that design beside its closest model at "
+    ap.add_argument("--design", default=None, help="tugelorn (beside Qwen3), dufizen (beside Tugelorn), burolorn (beside Qwen3) or gevovik (beside Tugelorn): that design beside its closest model at "
                                                    "equal layer sizes")
     ap.add_argument("--design-sizes", default="mid,8b", help="layer sizes of --design: " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--design-profile", action="store_true", help="with --design: a prompt and four eager decode steps")

@@ -15,9 +15,19 @@
 //                             heads' rows in shared memory.  With `num_splits` > 1 the key range of a token is cut
 //                             into pieces, one block each, which leave (maximum, sum, unnormalised rows) per head;
 //   attention_talking_merge   adds the pieces in a fixed order, folds the sink in and applies the gate.
+//   attention_talking_mma     portions of prompts in bfloat16 (head size 64 or 128, at most 16 heads): a block owns 16
+//                             neighbouring queries of a request and all heads, a warp per head.  32 keys at a time:
+//                             every warp takes its head's raw scores on mma.sync (m16n8k16, the keys of all kv heads
+//                             staged by cp.async, ldmatrix from swizzled rows) and leaves them in shared memory; after
+//                             the block has met, every warp mixes its head's scores from all heads' raw ones (float),
+//                             runs its softmax in the accumulator layout and multiplies the weights (rounded to
+//                             bfloat16 as the operand, like the package's other tensor-core attention) with the staged
+//                             values.  The next keys arrive while scores are mixed, the next values while raw scores
+//                             are taken.
 //
 // Scores, mixing, maxima, sums and weights are float whatever the storage type.
 #include "common.cuh"
+#include "mma_common.cuh"
 #include <math_constants.h>
 
 using namespace ccb;
@@ -122,7 +132,8 @@ attention_talking_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
         const T* kp = k_cache + ((size_t)krow + (size_t)(g / group) * page_size) * hd;
         const float* qg = qs + (size_t)g * hd;
         float s0 = 0.f, s1 = 0.f;
-        for (int i = 0; i < hd; i += 8) {
+#pragma unroll 4
+        for (int i = 0; i < hd; i += 8) {   // (the loads of several rounds are in flight together)
           float kv[8];
           Row8<T>::load(kp + i, kv);
 #pragma unroll
@@ -158,11 +169,13 @@ attention_talking_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
       const size_t vhead = (size_t)(h / group) * page_size;
       for (int c = lane; c < hd; c += 32) {
         float acc = os[(size_t)h * hd + c] * corr;
+        // a key that is not seen has weight 0 and reads the first row of its kv head's first page instead: no
+        // branch stands between the loads, so eight of them are in flight at a time
+#pragma unroll 8
         for (int kk = 0; kk < kTalkKeys; ++kk) {
           const float pk = pw[h * kTalkKeys + kk];
           const int vr = krows[kk];
-          if (pk == 0.f || vr < 0) continue;   // the same for every lane
-          acc = fmaf(pk, to_f32(v_cache[((size_t)vr + vhead) * hd + c]), acc);
+          acc = fmaf(pk, to_f32(v_cache[((size_t)(vr < 0 ? 0 : vr) + vhead) * hd + c]), acc);
         }
         os[(size_t)h * hd + c] = acc;
       }
@@ -189,36 +202,63 @@ attention_talking_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
   }
 }
 
-// out[t, h, :] = gate * sum_s acc_s exp(m_s - M) / (sum_s l_s exp(m_s - M) [+ exp(sink - M)]); a warp per (t, h).
+// out[t, h, :] = gate * sum_s acc_s exp(m_s - M) / (sum_s l_s exp(m_s - M) [+ exp(sink - M)]); a block per (t, h):
+// its first warp turns the pieces' maxima and sums into one weight per piece (at most 64 pieces), then every thread
+// adds its coordinates over the pieces in their order.
+constexpr int kMergeThreads = 128;
+constexpr int kMaxSplits = 64;
+
 template <typename T>
-__global__ void attention_talking_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
-                                               const float* __restrict__ part_ml, int rows, int nq, int hd,
-                                               int num_splits, AttnExtra ex) {
+__global__ void __launch_bounds__(kMergeThreads)
+attention_talking_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
+                               const float* __restrict__ part_ml, int rows, int nq, int hd, int num_splits,
+                               AttnExtra ex) {
   ccb::pdl_begin();
-  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (unit >= rows * nq) return;
+  __shared__ float wsplit[kMaxSplits];
+  __shared__ float mul_s;
+  const int t = blockIdx.x / nq, h = blockIdx.x - t * nq;
   const int lane = threadIdx.x & 31;
-  const int t = unit / nq, h = unit - t * nq;
-  float M = -CUDART_INF_F;
-  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(((size_t)t * num_splits + s) * nq + h) * 2]);
-  T* orow = out + ((size_t)t * nq + h) * hd;
-  if (M == -CUDART_INF_F) {
-    for (int c = lane; c < hd; c += 32) orow[c] = from_f32<T>(0.f);
-    return;
-  }
-  float ll = 0.f;
-  for (int s = 0; s < num_splits; ++s) {
-    const float* pm = part_ml + (((size_t)t * num_splits + s) * nq + h) * 2;
-    if (pm[0] != -CUDART_INF_F) ll += pm[1] * expf(pm[0] - M);
-  }
-  const float f = attn_sink_fold(ex, h, M, ll);
-  const float mul = f * attn_gate<T>(ex, t, h) / ll;
-  for (int c = lane; c < hd; c += 32) {
-    float acc = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-      const float ms = part_ml[(((size_t)t * num_splits + s) * nq + h) * 2];
-      if (ms != -CUDART_INF_F) acc = fmaf(part_acc[(((size_t)t * num_splits + s) * nq + h) * hd + c], expf(ms - M), acc);
+  if (threadIdx.x < 32) {
+    float m[2], l[2];
+    float M = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int sp = lane + 32 * i;
+      m[i] = -CUDART_INF_F;
+      l[i] = 0.f;
+      if (sp < num_splits) {
+        const float2 v = *reinterpret_cast<const float2*>(part_ml + (((size_t)t * num_splits + sp) * nq + h) * 2);
+        m[i] = v.x;
+        l[i] = v.y;
+      }
+      M = fmaxf(M, m[i]);
     }
+    M = warp_max(M);
+    float ll = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float wgt = (m[i] == -CUDART_INF_F) ? 0.f : expf(m[i] - M);
+      if (lane + 32 * i < kMaxSplits) wsplit[lane + 32 * i] = wgt;
+      ll += l[i] * wgt;
+    }
+    ll = warp_sum(ll);
+    if (lane == 0) {
+      float mul = 0.f;
+      if (M != -CUDART_INF_F) {
+        const float f = attn_sink_fold(ex, h, M, ll);
+        mul = f * attn_gate<T>(ex, t, h) / ll;
+      }
+      mul_s = mul;
+    }
+  }
+  __syncthreads();
+  const float mul = mul_s;
+  T* orow = out + ((size_t)t * nq + h) * hd;
+  for (int c = threadIdx.x; c < hd; c += kMergeThreads) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int sp = 0; sp < num_splits; ++sp)
+      acc = fmaf(part_acc[(((size_t)t * num_splits + sp) * nq + h) * hd + c], wsplit[sp], acc);
     orow[c] = from_f32<T>(acc * mul);
   }
 }
@@ -239,9 +279,252 @@ int launch_talking(const void* q, const void* k_cache, const void* v_cache, void
              block_table, bt_stride, nq, nkv, hd, page_size, num_pages, window, num_splits, ex, status);
   int rc = ccb_launch_status();
   if (rc != 0 || num_splits == 1) return rc;
-  const int warps = 4;
-  ccb_launch(attention_talking_merge_kernel<T>, dim3((rows * nq + warps - 1) / warps), dim3(warps * 32), 0, stream,
-             (T*)out, (const float*)part_acc, (const float*)part_ml, rows, nq, hd, num_splits, ex);
+  ccb_launch(attention_talking_merge_kernel<T>, dim3(rows * nq), dim3(kMergeThreads), 0, stream, (T*)out,
+             (const float*)part_acc, (const float*)part_ml, rows, nq, hd, num_splits, ex);
+  return ccb_launch_status();
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Portions of prompts on tensor cores (bfloat16).  See the head of the file.
+constexpr int kMmaQ = 16;       // queries of a block
+constexpr int kMmaKeys = 32;    // keys staged at a time
+constexpr int kRawLd = 40;      // floats of a row of raw scores: 32 + 8, so that the 64-bit accesses of a half warp
+                                // (four rows, four columns pairs) fall into different banks
+
+template <int HD>
+__global__ void __launch_bounds__(512)
+attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                             const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
+                             const float* __restrict__ mix, const int* __restrict__ cu_q,
+                             const int* __restrict__ pos0, const int* __restrict__ block_table, int bt_stride,
+                             int entry0, int nq, int nkv, int page_size, int num_pages, int window, AttnExtra ex,
+                             int* status) {
+  ccb::pdl_begin();
+  constexpr int KS = HD / 16;   // k-steps over a head
+  constexpr int CH = HD / 8;    // 16-byte chunks of a row
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [nkv][32][HD], swizzled rows
+  __nv_bfloat16* v_s = k_s + (size_t)nkv * kMmaKeys * HD;                   // the same for the values
+  float* raw = reinterpret_cast<float*>(v_s + (size_t)nkv * kMmaKeys * HD);  // [nq][16][kRawLd]
+  float* ms = raw + (size_t)nq * kMmaQ * kRawLd;                             // [nq][nq]
+
+  const int b = entry0 + blockIdx.y;
+  const int row_begin = cu_q[b], n_new = cu_q[b + 1] - row_begin;
+  const int n_qtiles = (n_new + kMmaQ - 1) / kMmaQ;
+  const int qt = n_qtiles - 1 - (int)blockIdx.x;   // long tiles first
+  if (qt < 0) return;
+  const int tid = threadIdx.x, lane = tid & 31, h = tid >> 5;   // a warp per head
+  const int gid = lane >> 2, tig = lane & 3;
+  const int kvh = h / (nq / nkv);
+  const int q_first = qt * kMmaQ;
+  const int rows_here = min(kMmaQ, n_new - q_first);
+  const int p_first = pos0[b] + q_first, p_last = p_first + rows_here - 1;
+  const int* bt = block_table + (size_t)b * bt_stride;
+  const int j_lo = first_visible_key(p_first, window, 0);
+  const int first_tile = j_lo / kMmaKeys, n_tiles = p_last / kMmaKeys - first_tile + 1;
+  const int n_threads = nq * 32;
+
+  for (int i = tid; i < nq * nq; i += n_threads) ms[i] = mix[i];
+
+  // this head's query rows as A fragments, straight from global memory (rows beyond the portion are zero)
+  uint32_t qa[KS][4];
+  {
+    const bool ok0 = gid < rows_here, ok1 = gid + 8 < rows_here;
+    const __nv_bfloat16* q0 = q + ((size_t)(row_begin + q_first + (ok0 ? gid : 0)) * nq + h) * HD + 2 * tig;
+    const __nv_bfloat16* q1 = q + ((size_t)(row_begin + q_first + (ok1 ? gid + 8 : 0)) * nq + h) * HD + 2 * tig;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      qa[ks][0] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + 16 * ks) : 0u;
+      qa[ks][1] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + 16 * ks) : 0u;
+      qa[ks][2] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + 16 * ks + 8) : 0u;
+      qa[ks][3] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + 16 * ks + 8) : 0u;
+    }
+  }
+
+  // a tile of keys (or values) of every kv head: row r = kv head * 32 + key, its 16-byte chunks swizzled
+  auto issue = [&](const __nv_bfloat16* cache, __nv_bfloat16* dst, int tile) {
+    const int total = nkv * kMmaKeys * CH;
+    for (int i = tid; i < total; i += n_threads) {
+      const int r = i / CH, c = i - r * CH;
+      const int kh = r / kMmaKeys, j = tile * kMmaKeys + (r - kh * kMmaKeys);
+      bool valid = j >= j_lo && j <= p_last;
+      size_t src = 0;
+      if (valid) {
+        const int lp = j / page_size;
+        const int page = lp < bt_stride ? bt[lp] : -1;
+        if (page < 0 || page >= num_pages) {
+          set_status(status, CCB_ST_BAD_PAGE);
+          valid = false;
+        } else {
+          src = (((size_t)page * nkv + kh) * page_size + (j - lp * page_size)) * HD + c * 8;
+        }
+      }
+      cp_async16(smem_u32(dst + swz<HD>(r, c)), cache + src, valid);
+    }
+  };
+
+  const int pr0 = p_first + gid, pr1 = pr0 + 8;
+  const int lo0 = first_visible_key(pr0, window, 0), lo1 = first_visible_key(pr1, window, 0);
+  const bool live0 = gid < rows_here, live1 = gid + 8 < rows_here;
+
+  float o[2 * KS][4];
+#pragma unroll
+  for (int i = 0; i < 2 * KS; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+
+  issue(k_cache, k_s, first_tile);
+  cp_async_commit();
+  const float* mh = ms + (size_t)h * nq;
+  float* my_raw = raw + (size_t)h * kMmaQ * kRawLd;
+  const __nv_bfloat16* k_h = k_s + (size_t)kvh * kMmaKeys * HD;
+  const __nv_bfloat16* v_h = v_s + (size_t)kvh * kMmaKeys * HD;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int jt = (first_tile + it) * kMmaKeys;
+    cp_async_wait<0>();
+    __syncthreads();   // the keys of this tile are there; everybody is done with the values of the tile before
+    issue(v_cache, v_s, first_tile + it);
+    cp_async_commit();
+    // raw scores of this head: S [16 x 32] = Q K^T
+    float sc[4][4];
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
+    {
+      const int krow = (lane & 7) + 8 * (lane >> 4);
+      const int kchunk = (lane >> 3) & 1;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {
+          uint32_t b00, b01, b10, b11;
+          ldmatrix_x4(b00, b01, b10, b11, smem_u32(k_h + swz<HD>(np * 16 + krow, 2 * ks + kchunk)));
+          mma_bf16_16816(sc[2 * np], qa[ks], b00, b01);
+          mma_bf16_16816(sc[2 * np + 1], qa[ks], b10, b11);
+        }
+      }
+    }
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+      *reinterpret_cast<float2*>(my_raw + gid * kRawLd + nb * 8 + 2 * tig) = make_float2(sc[nb][0], sc[nb][1]);
+      *reinterpret_cast<float2*>(my_raw + (gid + 8) * kRawLd + nb * 8 + 2 * tig) = make_float2(sc[nb][2], sc[nb][3]);
+    }
+    __syncthreads();   // every head's raw scores are there; the keys' buffer is free
+    if (it + 1 < n_tiles) issue(k_cache, k_s, first_tile + it + 1);
+    cp_async_commit();
+    // this head's scores: the mix of all heads' raw ones (float), in the accumulator's layout
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
+    for (int g = 0; g < nq; ++g) {
+      const float wgt = mh[g];
+      const float* rg = raw + (size_t)g * kMmaQ * kRawLd;
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+        const float2 a = *reinterpret_cast<const float2*>(rg + gid * kRawLd + nb * 8 + 2 * tig);
+        const float2 c = *reinterpret_cast<const float2*>(rg + (gid + 8) * kRawLd + nb * 8 + 2 * tig);
+        sc[nb][0] = fmaf(wgt, a.x, sc[nb][0]);
+        sc[nb][1] = fmaf(wgt, a.y, sc[nb][1]);
+        sc[nb][2] = fmaf(wgt, c.x, sc[nb][2]);
+        sc[nb][3] = fmaf(wgt, c.y, sc[nb][3]);
+      }
+    }
+    float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = jt + nb * 8 + 2 * tig + e;
+        sc[nb][e] = (live0 && j <= pr0 && j >= lo0) ? sc[nb][e] : -CUDART_INF_F;
+        sc[nb][2 + e] = (live1 && j <= pr1 && j >= lo1) ? sc[nb][2 + e] : -CUDART_INF_F;
+        mx0 = fmaxf(mx0, sc[nb][e]);
+        mx1 = fmaxf(mx1, sc[nb][2 + e]);
+      }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float c0 = mn0 == -CUDART_INF_F ? 1.f : expf(m0 - mn0);
+    const float c1 = mn1 == -CUDART_INF_F ? 1.f : expf(m1 - mn1);
+    const float sub0 = mn0 == -CUDART_INF_F ? 0.f : mn0, sub1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
+    m0 = mn0;
+    m1 = mn1;
+    float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        sc[nb][e] = expf(sc[nb][e] - sub0);
+        sc[nb][2 + e] = expf(sc[nb][2 + e] - sub1);
+        ps0 += sc[nb][e];
+        ps1 += sc[nb][2 + e];
+      }
+    l0 = l0 * c0 + ps0;
+    l1 = l1 * c1 + ps1;
+#pragma unroll
+    for (int i = 0; i < 2 * KS; ++i) {
+      o[i][0] *= c0; o[i][1] *= c0;
+      o[i][2] *= c1; o[i][3] *= c1;
+    }
+    cp_async_wait<1>();   // the values (the keys of the next tile may still be on their way)
+    __syncthreads();
+    {
+      const int vrow = (lane & 7) + 8 * ((lane >> 3) & 1);
+      const int vchunk = lane >> 4;
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {   // 16 keys at a time
+        uint32_t pa[4];
+        pa[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+        pa[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+        pa[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+        pa[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+        for (int nn = 0; nn < KS; ++nn) {
+          uint32_t b00, b01, b10, b11;
+          ldmatrix_x4_trans(b00, b01, b10, b11, smem_u32(v_h + swz<HD>(kk * 16 + vrow, 2 * nn + vchunk)));
+          mma_bf16_16816(o[2 * nn], pa, b00, b01);
+          mma_bf16_16816(o[2 * nn + 1], pa, b10, b11);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float f0 = attn_sink_fold(ex, h, m0, l0), f1 = attn_sink_fold(ex, h, m1, l1);
+  float inv0 = l0 > 0.f ? f0 / l0 : 0.f, inv1 = l1 > 0.f ? f1 / l1 : 0.f;
+  if (live0) inv0 *= attn_gate<__nv_bfloat16>(ex, row_begin + q_first + gid, h);
+  if (live1) inv1 *= attn_gate<__nv_bfloat16>(ex, row_begin + q_first + gid + 8, h);
+  __nv_bfloat16* o0 = out + ((size_t)(row_begin + q_first + gid) * nq + h) * HD;
+  __nv_bfloat16* o1 = out + ((size_t)(row_begin + q_first + gid + 8) * nq + h) * HD;
+#pragma unroll
+  for (int i = 0; i < 2 * KS; ++i) {
+    const int d = i * 8 + 2 * tig;
+    if (live0) *reinterpret_cast<uint32_t*>(o0 + d) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+    if (live1) *reinterpret_cast<uint32_t*>(o1 + d) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+  }
+}
+
+size_t talking_mma_smem(int nq, int nkv, int hd) {
+  return (size_t)2 * nkv * kMmaKeys * hd * sizeof(__nv_bfloat16) + (size_t)nq * kMmaQ * kRawLd * sizeof(float) +
+         (size_t)nq * nq * sizeof(float);
+}
+
+template <int HD>
+int launch_talking_mma(const void* q, const void* k_cache, const void* v_cache, void* out, const float* mix,
+                       const int* cu_q, const int* pos0, const int* block_table, int bt_stride, int entry0,
+                       int n_entries, int max_new, int nq, int nkv, int page_size, int num_pages, int window,
+                       AttnExtra ex, int* status, cudaStream_t stream) {
+  const size_t smem = talking_mma_smem(nq, nkv, HD);
+  cudaError_t e = cudaFuncSetAttribute(attention_talking_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid((max_new + kMmaQ - 1) / kMmaQ, n_entries);
+  ccb_launch(attention_talking_mma_kernel<HD>, grid, dim3(nq * 32), smem, stream, (const __nv_bfloat16*)q,
+             (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, mix, cu_q, pos0,
+             block_table, bt_stride, entry0, nq, nkv, page_size, num_pages, window, ex, status);
   return ccb_launch_status();
 }
 
@@ -258,7 +541,7 @@ CCB_API int ccb_attention_talking(const void* q, const void* k_cache, const void
                                   int page_size, int num_pages, int window, int num_splits, const float* sink,
                                   const void* gate, int gate_stride, int dtype, int* status, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (!ccb_attention_talking_fits(nq, nkv, hd) || page_size <= 0 || window < 0 || num_splits < 1 || num_splits > 65535)
+  if (!ccb_attention_talking_fits(nq, nkv, hd) || page_size <= 0 || window < 0 || num_splits < 1 || num_splits > kMaxSplits)
     return CCB_REFUSE_SIZE;
   if (mix == nullptr || (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr))) return CCB_REFUSE_ARG;
   AttnExtra ex{0, sink, gate, gate_stride};
@@ -271,4 +554,29 @@ CCB_API int ccb_attention_talking(const void* q, const void* k_cache, const void
                                          block_table, bt_stride, rows, nq, nkv, hd, page_size, num_pages, window,
                                          num_splits, ex, status, stream);
   return CCB_REFUSE_DTYPE;
+}
+
+// The tensor-core form for portions of prompts: bfloat16, head size 64 or 128, at most 16 heads (a warp each), and
+// shared memory for a tile of keys and of values of every kv head.
+CCB_API int ccb_attention_talking_mma_fits(int nq, int nkv, int hd) {
+  return nq > 0 && nq <= 16 && nkv > 0 && nq % nkv == 0 && (hd == 64 || hd == 128) &&
+         talking_mma_smem(nq, nkv, hd) <= 220 * 1024;
+}
+
+// Requests entry0 .. entry0 + n_entries - 1 of the step (none with more than max_new tokens); bfloat16.
+CCB_API int ccb_attention_talking_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                      const float* mix, const int* cu_q, const int* pos0, const int* block_table,
+                                      int bt_stride, int entry0, int n_entries, int max_new, int nq, int nkv, int hd,
+                                      int page_size, int num_pages, int window, const float* sink, const void* gate,
+                                      int gate_stride, int* status, cudaStream_t stream) {
+  if (n_entries <= 0 || max_new <= 0) return 0;
+  if (!ccb_attention_talking_mma_fits(nq, nkv, hd) || page_size <= 0 || window < 0 || n_entries > 65535)
+    return CCB_REFUSE_SIZE;
+  if (mix == nullptr || (gate != nullptr && gate_stride < nq)) return CCB_REFUSE_ARG;
+  AttnExtra ex{0, sink, gate, gate_stride};
+  if (hd == 128)
+    return launch_talking_mma<128>(q, k_cache, v_cache, out, mix, cu_q, pos0, block_table, bt_stride, entry0,
+                                   n_entries, max_new, nq, nkv, page_size, num_pages, window, ex, status, stream);
+  return launch_talking_mma<64>(q, k_cache, v_cache, out, mix, cu_q, pos0, block_table, bt_stride, entry0, n_entries,
+                                max_new, nq, nkv, page_size, num_pages, window, ex, status, stream);
 }

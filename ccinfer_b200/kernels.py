@@ -168,6 +168,8 @@ _SIGNATURES = {
     "ccb_ssm_recurrence": [c_void_p] * 9 + [c_int] * 5 + [c_void_p],
     "ccb_attention_talking_fits": [c_int, c_int, c_int],
     "ccb_attention_talking": [c_void_p] * 10 + [c_int] * 9 + [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "ccb_attention_talking_mma_fits": [c_int, c_int, c_int],
+    "ccb_attention_talking_mma": [c_void_p] * 8 + [c_int] * 10 + [c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "ccb_embed_pair": [c_void_p] * 10 + [c_float] + [c_int] * 9 + [c_void_p, c_int, c_void_p, c_void_p],
     "ccb_relu_squared": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
     "ccb_scaled_sum": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_longlong, c_int, c_void_p],
@@ -937,6 +939,29 @@ def attention_talking(q, k_cache, v_cache, out, mix, positions, entry_of_token, 
                                        _stream()), "attention_talking")
     if num_splits > 1:
         counters.own += 1   # the merge kernel
+
+
+def attention_talking_mma_fits(dtype, nq: int, nkv: int, hd: int) -> bool:
+    """Whether the tensor-core form of the talking-heads attention takes these sizes (portions of prompts)."""
+    return dtype == torch.bfloat16 and bool(lib().ccb_attention_talking_mma_fits(int(nq), int(nkv), int(hd)))
+
+
+def attention_talking_mma(q, k_cache, v_cache, out, mix, cu_q, pos0, block_table, entry0: int, n_entries: int,
+                          max_q: int, window: int, sink=None, gate=None, status=None) -> None:
+    """``attention_talking`` for the step's entries entry0 .. entry0 + n_entries - 1 (none with more than ``max_q``
+    tokens) on tensor cores: bfloat16, see attention_talking_mma_fits."""
+    _cuda(q, k_cache, v_cache, out, mix, cu_q, pos0, block_table, sink, status)
+    T, nq, hd = q.shape
+    nkv, page_size = k_cache.shape[1], k_cache.shape[2]
+    assert out.shape == q.shape and k_cache.shape == v_cache.shape and k_cache.shape[3] == hd
+    assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16 and mix.dtype == torch.float32
+    assert mix.shape == (nq, nq) and (sink is None or (sink.dtype == torch.float32 and sink.numel() == nq))
+    assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1)
+    _check(lib().ccb_attention_talking_mma(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(mix), _p(cu_q), _p(pos0),
+                                           _p(block_table), block_table.stride(0), int(entry0), int(n_entries),
+                                           int(max_q), nq, nkv, hd, page_size, k_cache.shape[0], int(window), _p(sink),
+                                           _p(gate), gate.stride(0) if gate is not None else 0, _p(status), _stream()),
+           "attention_talking_mma")
 
 
 def concat_cast(out, a, b) -> None:

@@ -263,15 +263,26 @@ class GroupedQueryAttention(Mixer):
         rt, g = self.rt, cache.group
         if self.talking:
             # every head's weights need every head's scores: one kernel owns all heads of a query
-            splits = kernels.attention_talking_splits(T, self.window or 0)
-            acc = ml = None
-            if splits > 1:   # (rows x pieces never exceeds the number of blocks aimed for)
-                most = kernels.split_target_blocks()
-                acc = rt.scratch.get("talk_part_acc", (most * self.nq * self.hd,), torch.float32)
-                ml = rt.scratch.get("talk_part_ml", (most * self.nq * 2,), torch.float32)
-            kernels.attention_talking(q, cache.k, cache.v, o, self.mix, step.positions, step.entry_of_token,
-                                      g.block_table, self.window or 0, splits, acc, ml, sink=self.sink, gate=gate,
-                                      status=rt.status)
+            # portions of prompts: the tensor-core form where it takes the sizes; single tokens (and everything
+            # else): the kernel with a block per token, the key range in pieces when rows are few
+            many = step.n_entries - step.n_single
+            tc = many > 0 and kernels.attention_talking_mma_fits(rt.dtype, self.nq, self.nkv, self.hd)
+            n_rows = step.n_single if tc else T
+            if n_rows > 0:
+                splits = kernels.attention_talking_splits(n_rows, self.window or 0)
+                acc = ml = None
+                if splits > 1:   # (rows x pieces never exceeds the number of blocks aimed for)
+                    most = kernels.split_target_blocks()
+                    acc = rt.scratch.get("talk_part_acc", (most * self.nq * self.hd,), torch.float32)
+                    ml = rt.scratch.get("talk_part_ml", (most * self.nq * 2,), torch.float32)
+                kernels.attention_talking(q[:n_rows], cache.k, cache.v, o[:n_rows], self.mix, step.positions,
+                                          step.entry_of_token, g.block_table, self.window or 0, splits, acc, ml,
+                                          sink=self.sink, gate=gate[:n_rows] if gate is not None else None,
+                                          status=rt.status)
+            if tc:
+                kernels.attention_talking_mma(q, cache.k, cache.v, o, self.mix, step.cu_q, step.pos0, g.block_table,
+                                              step.n_single, many, step.max_q_len, self.window or 0, sink=self.sink,
+                                              gate=gate, status=rt.status)
             return
         mma = rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES and not self.float_weights
         extra = {"chunk": self.chunk, "sink": self.sink, "gate": gate} if self.extras else {}

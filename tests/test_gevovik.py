@@ -258,6 +258,54 @@ def test_talking_attention_kernel(dtype, shape):
         assert err < (2e-5 if dtype == torch.float32 else 3e-2), (shape, splits, float(err))
 
 
+@gpu
+@pytest.mark.parametrize("shape", [(16, 8, 128, 40), (4, 2, 64, 0), (6, 2, 64, 9), (12, 4, 128, 33), (1, 1, 64, 1)])
+def test_talking_attention_on_tensor_cores(shape):
+    """The tensor-core form for portions of prompts: two requests in one launch, one whole (70 tokens), one a
+    portion of 45 tokens after 25 cached ones, pages in a shuffled order, sink and gate."""
+    from ccinfer_b200 import kernels
+    nq, nkv, hd, window = shape
+    assert kernels.attention_talking_mma_fits(torch.bfloat16, nq, nkv, hd)
+    g = torch.Generator().manual_seed(nq * 100 + hd)
+    T, page, dtype = 70, 8, torch.bfloat16
+    rep = nq // nkv
+    mix = (torch.eye(nq) + 0.4 * torch.randn(nq, nq, generator=g)) * (1.5 / math.sqrt(hd))
+    sink = torch.randn(nq, generator=g)
+    n_pages = 24
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    seqs, wants = [], []
+    for _ in range(2):
+        q = torch.randn(T, nq, hd, generator=g).to(dtype)
+        k = torch.randn(T, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(T, nkv, hd, generator=g).to(dtype)
+        gate = torch.randn(T, nq + 3, generator=g).to(dtype)
+        s = torch.einsum("ihd,jhd->hij", q.double(), k.double().repeat_interleave(rep, 1))
+        s = torch.einsum("hg,gij->hij", mix.double(), s)
+        i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+        seen = (j <= i) & ((i - j < window) if window else True)
+        s = s.masked_fill(~seen[None], float("-inf"))
+        s = torch.cat([s, sink.double()[:, None, None].expand(nq, T, 1)], -1)
+        a = torch.softmax(s, -1)[..., :T]
+        want = torch.einsum("hij,jhd->ihd", a, v.double().repeat_interleave(rep, 1))
+        wants.append(want * torch.sigmoid(gate.double()[:, :nq])[:, :, None])
+        seqs.append((q, k, v, gate))
+    kc = _paged(seqs[0][1], page, n_pages, perm[:12]) + _paged(seqs[1][1], page, n_pages, perm[12:])
+    vc = _paged(seqs[0][2], page, n_pages, perm[:12]) + _paged(seqs[1][2], page, n_pages, perm[12:])
+    bt = torch.full((2, 16), -1, dtype=torch.int32)
+    bt[0, :12] = torch.tensor(perm[:12], dtype=torch.int32)
+    bt[1, :12] = torch.tensor(perm[12:], dtype=torch.int32)
+    q = torch.cat([seqs[0][0], seqs[1][0][25:]]).cuda()
+    gate = torch.cat([seqs[0][3], seqs[1][3][25:]]).cuda()
+    want = torch.cat([wants[0], wants[1][25:]])
+    out = torch.full(tuple(q.shape), float("nan"), dtype=dtype, device="cuda")
+    cu = torch.tensor([0, 70, 115], dtype=torch.int32).cuda()
+    pos0 = torch.tensor([0, 25], dtype=torch.int32).cuda()
+    kernels.attention_talking_mma(q, kc.cuda(), vc.cuda(), out, mix.cuda(), cu, pos0, bt.cuda(), 0, 2, 70, window,
+                                  sink=sink.cuda(), gate=gate)
+    err = (out.cpu().double() - want).abs().max()
+    assert err < 3e-2, (shape, float(err))
+
+
 # ---------------------------------------------------------------------------------------------
 # GPU: each mixer as the only layer of a model
 # ---------------------------------------------------------------------------------------------
@@ -270,6 +318,9 @@ ALONE = {
         plain.delta(2, 2, 8, 8, 3), 0.6, 1.4),
     "unequal head sizes, part of the head rotated, no mask": plain.pair(
         plain.talking(3, 1, 20, 12, 0.3, rot=(6, 50.0)), plain.delta(1, 1, 6, 10, 2), 1.0, 1.0),
+    "talking attention at tensor-core sizes": plain.pair(
+        plain.talking(8, 4, 64, 64, 0.125, window=40, rot=(32, 10000.0), scaling=(2.0, 16, 4.0, 1.0)),
+        plain.delta(2, 1, 16, 16, 4), 1.0, 0.3),
     "latent attention": plain.latent(3, 8, 4, 8, 16, 0.3),
     "latent attention, tensor-core sizes": plain.latent(4, 16, 16, 32, 64, 0.2),
 }
