@@ -57,6 +57,19 @@ template <> struct Row8<__nv_bfloat16> {
   }
 };
 
+template <typename T> struct Row4;   // four neighbouring elements as floats
+template <> struct Row4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+};
+template <> struct Row4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 a = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+  }
+};
+
 // q, out [T, nq, hd]; k_cache, v_cache [pages, nkv, page_size, hd]; mix float [nq, nq].
 // part_acc [T, splits, nq, hd], part_ml [T, splits, nq, 2] (only with num_splits > 1).
 template <typename T>
@@ -132,7 +145,7 @@ attention_talking_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
         const T* kp = k_cache + ((size_t)krow + (size_t)(g / group) * page_size) * hd;
         const float* qg = qs + (size_t)g * hd;
         float s0 = 0.f, s1 = 0.f;
-#pragma unroll 4
+#pragma unroll 8
         for (int i = 0; i < hd; i += 8) {   // (the loads of several rounds are in flight together)
           float kv[8];
           Row8<T>::load(kp + i, kv);
@@ -167,17 +180,23 @@ attention_talking_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
         run_l[h] = l_new;
       }
       const size_t vhead = (size_t)(h / group) * page_size;
-      for (int c = lane; c < hd; c += 32) {
-        float acc = os[(size_t)h * hd + c] * corr;
-        // a key that is not seen has weight 0 and reads the first row of its kv head's first page instead: no
-        // branch stands between the loads, so eight of them are in flight at a time
+      // four neighbouring coordinates a lane (a head of 128 is one pass of the warp over a value row).  A key that
+      // is not seen has weight 0 and reads the first row of its kv head's first page instead: no branch stands
+      // between the loads, so eight rows are in flight at a time
+      for (int c = 4 * lane; c < hd; c += 128) {
+        float4 acc = *reinterpret_cast<float4*>(os + (size_t)h * hd + c);
+        acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
 #pragma unroll 8
         for (int kk = 0; kk < kTalkKeys; ++kk) {
           const float pk = pw[h * kTalkKeys + kk];
           const int vr = krows[kk];
-          acc = fmaf(pk, to_f32(v_cache[((size_t)(vr < 0 ? 0 : vr) + vhead) * hd + c]), acc);
+          const float4 vv = Row4<T>::load(v_cache + ((size_t)(vr < 0 ? 0 : vr) + vhead) * hd + c);
+          acc.x = fmaf(pk, vv.x, acc.x);
+          acc.y = fmaf(pk, vv.y, acc.y);
+          acc.z = fmaf(pk, vv.z, acc.z);
+          acc.w = fmaf(pk, vv.w, acc.w);
         }
-        os[(size_t)h * hd + c] = acc;
+        *reinterpret_cast<float4*>(os + (size_t)h * hd + c) = acc;
       }
       __syncwarp();
     }
@@ -289,8 +308,10 @@ int launch_talking(const void* q, const void* k_cache, const void* v_cache, void
 // Portions of prompts on tensor cores (bfloat16).  See the head of the file.
 constexpr int kMmaQ = 16;       // queries of a block
 constexpr int kMmaKeys = 32;    // keys staged at a time
-constexpr int kRawLd = 40;      // floats of a row of raw scores: 32 + 8, so that the 64-bit accesses of a half warp
-                                // (four rows, four columns pairs) fall into different banks
+constexpr int kRawLd = 36;      // floats of a row of raw scores.  A thread's eight values of a row (its two columns of
+                                // each of the four 8-key blocks) lie side by side, at 8 tig + 2 block + e, and are
+                                // moved 16 bytes at a time; with 32 + 4 floats a row the eight threads of such an
+                                // access (two rows, four tig) fall into different banks
 
 template <int HD>
 __global__ void __launch_bounds__(512)
@@ -325,7 +346,8 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   const int first_tile = j_lo / kMmaKeys, n_tiles = p_last / kMmaKeys - first_tile + 1;
   const int n_threads = nq * 32;
 
-  for (int i = tid; i < nq * nq; i += n_threads) ms[i] = mix[i];
+  // (the mixing matrix times log2(e): the softmax runs on base-2 exponentials, one instruction each)
+  for (int i = tid; i < nq * nq; i += n_threads) ms[i] = mix[i] * 1.4426950408889634f;
 
   // this head's query rows as A fragments, straight from global memory (rows beyond the portion are zero)
   uint32_t qa[KS][4];
@@ -343,30 +365,34 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   }
 
   // a tile of keys (or values) of every kv head: row r = kv head * 32 + key, its 16-byte chunks swizzled
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
   auto issue = [&](const __nv_bfloat16* cache, __nv_bfloat16* dst, int tile) {
-    const int total = nkv * kMmaKeys * CH;
-    for (int i = tid; i < total; i += n_threads) {
-      const int r = i / CH, c = i - r * CH;
-      const int kh = r / kMmaKeys, j = tile * kMmaKeys + (r - kh * kMmaKeys);
+    for (int i = tid; i < kMmaKeys * CH; i += n_threads) {   // (key of the tile, chunk): the page is looked up once
+      const int kr = i / CH, c = i - kr * CH;
+      const int j = tile * kMmaKeys + kr;
       bool valid = j >= j_lo && j <= p_last;
       size_t src = 0;
       if (valid) {
-        const int lp = j / page_size;
+        const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
         const int page = lp < bt_stride ? bt[lp] : -1;
         if (page < 0 || page >= num_pages) {
           set_status(status, CCB_ST_BAD_PAGE);
           valid = false;
         } else {
-          src = (((size_t)page * nkv + kh) * page_size + (j - lp * page_size)) * HD + c * 8;
+          src = ((size_t)page * nkv * page_size + (j - lp * page_size)) * HD + c * 8;
         }
       }
-      cp_async16(smem_u32(dst + swz<HD>(r, c)), cache + src, valid);
+      const uint32_t d0 = smem_u32(dst + swz<HD>(kr, c));   // (32 rows a kv head: the swizzle is the same for each)
+      const size_t head_stride = (size_t)page_size * HD;
+      for (int kh = 0; kh < nkv; ++kh)
+        cp_async16(d0 + (uint32_t)(kh * kMmaKeys * HD * 2), cache + src + kh * head_stride, valid);
     }
   };
 
   const int pr0 = p_first + gid, pr1 = pr0 + 8;
   const int lo0 = first_visible_key(pr0, window, 0), lo1 = first_visible_key(pr1, window, 0);
   const bool live0 = gid < rows_here, live1 = gid + 8 < rows_here;
+  const int lo_last = first_visible_key(p_last, window, 0);   // (the first key that the block's last row sees)
 
   float o[2 * KS][4];
 #pragma unroll
@@ -405,9 +431,11 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
       }
     }
 #pragma unroll
-    for (int nb = 0; nb < 4; ++nb) {
-      *reinterpret_cast<float2*>(my_raw + gid * kRawLd + nb * 8 + 2 * tig) = make_float2(sc[nb][0], sc[nb][1]);
-      *reinterpret_cast<float2*>(my_raw + (gid + 8) * kRawLd + nb * 8 + 2 * tig) = make_float2(sc[nb][2], sc[nb][3]);
+    for (int half = 0; half < 2; ++half) {
+      float* r0p = my_raw + gid * kRawLd + 8 * tig + 4 * half;
+      float* r1p = my_raw + (gid + 8) * kRawLd + 8 * tig + 4 * half;
+      *reinterpret_cast<float4*>(r0p) = make_float4(sc[2 * half][0], sc[2 * half][1], sc[2 * half + 1][0], sc[2 * half + 1][1]);
+      *reinterpret_cast<float4*>(r1p) = make_float4(sc[2 * half][2], sc[2 * half][3], sc[2 * half + 1][2], sc[2 * half + 1][3]);
     }
     __syncthreads();   // every head's raw scores are there; the keys' buffer is free
     if (it + 1 < n_tiles) issue(k_cache, k_s, first_tile + it + 1);
@@ -415,27 +443,43 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     // this head's scores: the mix of all heads' raw ones (float), in the accumulator's layout
 #pragma unroll
     for (int nb = 0; nb < 4; ++nb) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
-    for (int g = 0; g < nq; ++g) {
-      const float wgt = mh[g];
-      const float* rg = raw + (size_t)g * kMmaQ * kRawLd;
+    {
+      const float* rg = raw + gid * kRawLd + 8 * tig;
+#pragma unroll 4
+      for (int g = 0; g < nq; ++g, rg += kMmaQ * kRawLd) {
+        const float wgt = mh[g];
 #pragma unroll
-      for (int nb = 0; nb < 4; ++nb) {
-        const float2 a = *reinterpret_cast<const float2*>(rg + gid * kRawLd + nb * 8 + 2 * tig);
-        const float2 c = *reinterpret_cast<const float2*>(rg + (gid + 8) * kRawLd + nb * 8 + 2 * tig);
-        sc[nb][0] = fmaf(wgt, a.x, sc[nb][0]);
-        sc[nb][1] = fmaf(wgt, a.y, sc[nb][1]);
-        sc[nb][2] = fmaf(wgt, c.x, sc[nb][2]);
-        sc[nb][3] = fmaf(wgt, c.y, sc[nb][3]);
+        for (int half = 0; half < 2; ++half) {
+          const float4 a = *reinterpret_cast<const float4*>(rg + 4 * half);
+          const float4 c = *reinterpret_cast<const float4*>(rg + 8 * kRawLd + 4 * half);
+          sc[2 * half][0] = fmaf(wgt, a.x, sc[2 * half][0]);
+          sc[2 * half][1] = fmaf(wgt, a.y, sc[2 * half][1]);
+          sc[2 * half + 1][0] = fmaf(wgt, a.z, sc[2 * half + 1][0]);
+          sc[2 * half + 1][1] = fmaf(wgt, a.w, sc[2 * half + 1][1]);
+          sc[2 * half][2] = fmaf(wgt, c.x, sc[2 * half][2]);
+          sc[2 * half][3] = fmaf(wgt, c.y, sc[2 * half][3]);
+          sc[2 * half + 1][2] = fmaf(wgt, c.z, sc[2 * half + 1][2]);
+          sc[2 * half + 1][3] = fmaf(wgt, c.w, sc[2 * half + 1][3]);
+        }
       }
     }
     float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+    // a tile that every row of the block sees whole needs no mask (the same for all threads)
+    const bool inside = rows_here == kMmaQ && jt + kMmaKeys - 1 <= p_first && jt >= lo_last;
+    if (!inside) {
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int j = jt + nb * 8 + 2 * tig + e;
+          sc[nb][e] = (live0 && j <= pr0 && j >= lo0) ? sc[nb][e] : -CUDART_INF_F;
+          sc[nb][2 + e] = (live1 && j <= pr1 && j >= lo1) ? sc[nb][2 + e] : -CUDART_INF_F;
+        }
+    }
 #pragma unroll
     for (int nb = 0; nb < 4; ++nb)
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const int j = jt + nb * 8 + 2 * tig + e;
-        sc[nb][e] = (live0 && j <= pr0 && j >= lo0) ? sc[nb][e] : -CUDART_INF_F;
-        sc[nb][2 + e] = (live1 && j <= pr1 && j >= lo1) ? sc[nb][2 + e] : -CUDART_INF_F;
         mx0 = fmaxf(mx0, sc[nb][e]);
         mx1 = fmaxf(mx1, sc[nb][2 + e]);
       }
@@ -444,8 +488,8 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-    const float c0 = mn0 == -CUDART_INF_F ? 1.f : expf(m0 - mn0);
-    const float c1 = mn1 == -CUDART_INF_F ? 1.f : expf(m1 - mn1);
+    const float c0 = mn0 == -CUDART_INF_F ? 1.f : exp2f(m0 - mn0);
+    const float c1 = mn1 == -CUDART_INF_F ? 1.f : exp2f(m1 - mn1);
     const float sub0 = mn0 == -CUDART_INF_F ? 0.f : mn0, sub1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
     m0 = mn0;
     m1 = mn1;
@@ -454,8 +498,8 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     for (int nb = 0; nb < 4; ++nb)
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        sc[nb][e] = expf(sc[nb][e] - sub0);
-        sc[nb][2 + e] = expf(sc[nb][2 + e] - sub1);
+        sc[nb][e] = exp2f(sc[nb][e] - sub0);
+        sc[nb][2 + e] = exp2f(sc[nb][2 + e] - sub1);
         ps0 += sc[nb][e];
         ps1 += sc[nb][2 + e];
       }
@@ -493,7 +537,15 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  const float f0 = attn_sink_fold(ex, h, m0, l0), f1 = attn_sink_fold(ex, h, m1, l1);
+  float f0 = 1.f, f1 = 1.f;
+  if (ex.sink != nullptr) {   // one more term in each denominator (the maxima are in the base-2 scale of the scores)
+    const float sk = ex.sink[h] * 1.4426950408889634f;
+    const float n0 = fmaxf(m0, sk), n1 = fmaxf(m1, sk);
+    f0 = m0 == -CUDART_INF_F ? 0.f : exp2f(m0 - n0);
+    f1 = m1 == -CUDART_INF_F ? 0.f : exp2f(m1 - n1);
+    l0 = l0 * f0 + exp2f(sk - n0);
+    l1 = l1 * f1 + exp2f(sk - n1);
+  }
   float inv0 = l0 > 0.f ? f0 / l0 : 0.f, inv1 = l1 > 0.f ? f1 / l1 : 0.f;
   if (live0) inv0 *= attn_gate<__nv_bfloat16>(ex, row_begin + q_first + gid, h);
   if (live1) inv1 *= attn_gate<__nv_bfloat16>(ex, row_begin + q_first + gid + 8, h);
