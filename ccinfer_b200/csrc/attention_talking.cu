@@ -23,11 +23,14 @@
 //                             runs its softmax in the accumulator layout and multiplies the weights (rounded to
 //                             bfloat16 as the operand, like the package's other tensor-core attention) with the staged
 //                             values.  The next keys arrive while scores are mixed, the next values while raw scores
-//                             are taken.
+//                             are taken.  With 17 to 32 heads two blocks form a thread-block cluster: each owns half of
+//                             the heads (and stages only their kv heads) and reads the other half's raw scores from
+//                             its partner's shared memory (distributed shared memory) between two cluster barriers.
 //
 // Scores, mixing, maxima, sums and weights are float whatever the storage type.
 #include "common.cuh"
 #include "mma_common.cuh"
+#include <cooperative_groups.h>
 #include <math_constants.h>
 
 using namespace ccb;
@@ -313,7 +316,7 @@ constexpr int kRawLd = 36;      // floats of a row of raw scores.  A thread's ei
                                 // moved 16 bytes at a time; with 32 + 4 floats a row the eight threads of such an
                                 // access (two rows, four tig) fall into different banks
 
-template <int HD>
+template <int HD, int CL>
 __global__ void __launch_bounds__(512)
 attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                              const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
@@ -325,29 +328,41 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   constexpr int KS = HD / 16;   // k-steps over a head
   constexpr int CH = HD / 8;    // 16-byte chunks of a row
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [nkv][32][HD], swizzled rows
-  __nv_bfloat16* v_s = k_s + (size_t)nkv * kMmaKeys * HD;                   // the same for the values
-  float* raw = reinterpret_cast<float*>(v_s + (size_t)nkv * kMmaKeys * HD);  // [nq][16][kRawLd]
-  float* ms = raw + (size_t)nq * kMmaQ * kRawLd;                             // [nq][nq]
+  namespace cg = cooperative_groups;
+  // the block's heads: all of them, or with a cluster of CL blocks the rank's share (and their kv heads)
+  const int hpc = nq / CL, kv_local = nkv / CL;
+  int rank = 0;
+  if constexpr (CL > 1) rank = (int)cg::this_cluster().block_rank();
+  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);               // [kv_local][32][HD], swizzled rows
+  __nv_bfloat16* v_s = k_s + (size_t)kv_local * kMmaKeys * HD;                   // the same for the values
+  float* raw = reinterpret_cast<float*>(v_s + (size_t)kv_local * kMmaKeys * HD);  // [hpc][16][kRawLd]
+  float* ms = raw + (size_t)hpc * kMmaQ * kRawLd;                                 // [hpc][nq]: the rows of its heads
+  const float* raw_of[CL];   // the raw scores of every block of the cluster (its own among them)
+  raw_of[0] = raw;
+  if constexpr (CL > 1) {
+#pragma unroll
+    for (int r = 0; r < CL; ++r) raw_of[r] = cg::this_cluster().map_shared_rank(raw, r);
+  }
 
   const int b = entry0 + blockIdx.y;
   const int row_begin = cu_q[b], n_new = cu_q[b + 1] - row_begin;
   const int n_qtiles = (n_new + kMmaQ - 1) / kMmaQ;
-  const int qt = n_qtiles - 1 - (int)blockIdx.x;   // long tiles first
+  const int qt = n_qtiles - 1 - (int)blockIdx.x / CL;   // long tiles first (the blocks of a cluster share a tile)
   if (qt < 0) return;
-  const int tid = threadIdx.x, lane = tid & 31, h = tid >> 5;   // a warp per head
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = rank * hpc + warp;                              // a warp per head
   const int gid = lane >> 2, tig = lane & 3;
-  const int kvh = h / (nq / nkv);
+  const int kvh = h / (nq / nkv) - rank * kv_local;             // among the kv heads staged here
   const int q_first = qt * kMmaQ;
   const int rows_here = min(kMmaQ, n_new - q_first);
   const int p_first = pos0[b] + q_first, p_last = p_first + rows_here - 1;
   const int* bt = block_table + (size_t)b * bt_stride;
   const int j_lo = first_visible_key(p_first, window, 0);
   const int first_tile = j_lo / kMmaKeys, n_tiles = p_last / kMmaKeys - first_tile + 1;
-  const int n_threads = nq * 32;
+  const int n_threads = hpc * 32;
 
   // (the mixing matrix times log2(e): the softmax runs on base-2 exponentials, one instruction each)
-  for (int i = tid; i < nq * nq; i += n_threads) ms[i] = mix[i] * 1.4426950408889634f;
+  for (int i = tid; i < hpc * nq; i += n_threads) ms[i] = mix[(size_t)rank * hpc * nq + i] * 1.4426950408889634f;
 
   // this head's query rows as A fragments, straight from global memory (rows beyond the portion are zero)
   uint32_t qa[KS][4];
@@ -379,12 +394,12 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
           set_status(status, CCB_ST_BAD_PAGE);
           valid = false;
         } else {
-          src = ((size_t)page * nkv * page_size + (j - lp * page_size)) * HD + c * 8;
+          src = (((size_t)page * nkv + rank * kv_local) * page_size + (j - lp * page_size)) * HD + c * 8;
         }
       }
       const uint32_t d0 = smem_u32(dst + swz<HD>(kr, c));   // (32 rows a kv head: the swizzle is the same for each)
       const size_t head_stride = (size_t)page_size * HD;
-      for (int kh = 0; kh < nkv; ++kh)
+      for (int kh = 0; kh < kv_local; ++kh)
         cp_async16(d0 + (uint32_t)(kh * kMmaKeys * HD * 2), cache + src + kh * head_stride, valid);
     }
   };
@@ -401,15 +416,17 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
 
   issue(k_cache, k_s, first_tile);
   cp_async_commit();
-  const float* mh = ms + (size_t)h * nq;
-  float* my_raw = raw + (size_t)h * kMmaQ * kRawLd;
+  const float* mh = ms + (size_t)warp * nq;
+  float* my_raw = raw + (size_t)warp * kMmaQ * kRawLd;
   const __nv_bfloat16* k_h = k_s + (size_t)kvh * kMmaKeys * HD;
   const __nv_bfloat16* v_h = v_s + (size_t)kvh * kMmaKeys * HD;
 
   for (int it = 0; it < n_tiles; ++it) {
     const int jt = (first_tile + it) * kMmaKeys;
     cp_async_wait<0>();
-    __syncthreads();   // the keys of this tile are there; everybody is done with the values of the tile before
+    // the keys of this tile are there; everybody is done with the values of the tile before (and, in a cluster,
+    // the partner is done with this block's raw scores of the tile before)
+    if constexpr (CL > 1) cg::this_cluster().sync(); else __syncthreads();
     issue(v_cache, v_s, first_tile + it);
     cp_async_commit();
     // raw scores of this head: S [16 x 32] = Q K^T
@@ -437,17 +454,20 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
       *reinterpret_cast<float4*>(r0p) = make_float4(sc[2 * half][0], sc[2 * half][1], sc[2 * half + 1][0], sc[2 * half + 1][1]);
       *reinterpret_cast<float4*>(r1p) = make_float4(sc[2 * half][2], sc[2 * half][3], sc[2 * half + 1][2], sc[2 * half + 1][3]);
     }
-    __syncthreads();   // every head's raw scores are there; the keys' buffer is free
+    // every head's raw scores are there (in a cluster: the partner's too); the keys' buffer is free
+    if constexpr (CL > 1) cg::this_cluster().sync(); else __syncthreads();
     if (it + 1 < n_tiles) issue(k_cache, k_s, first_tile + it + 1);
     cp_async_commit();
     // this head's scores: the mix of all heads' raw ones (float), in the accumulator's layout
 #pragma unroll
     for (int nb = 0; nb < 4; ++nb) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
-    {
-      const float* rg = raw + gid * kRawLd + 8 * tig;
+#pragma unroll
+    for (int r = 0; r < CL; ++r) {
+      const float* rg = raw_of[r] + gid * kRawLd + 8 * tig;
+      const float* mr = mh + r * hpc;
 #pragma unroll 4
-      for (int g = 0; g < nq; ++g, rg += kMmaQ * kRawLd) {
-        const float wgt = mh[g];
+      for (int g = 0; g < hpc; ++g, rg += kMmaQ * kRawLd) {
+        const float wgt = mr[g];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           const float4 a = *reinterpret_cast<const float4*>(rg + 4 * half);
@@ -533,6 +553,7 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     }
   }
   cp_async_wait<0>();
+  if constexpr (CL > 1) cg::this_cluster().sync();   // (the partner may still be reading this block's raw scores)
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -559,24 +580,46 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   }
 }
 
+int talking_mma_cluster(int nq) { return nq <= 16 ? 1 : 2; }
+
 size_t talking_mma_smem(int nq, int nkv, int hd) {
-  return (size_t)2 * nkv * kMmaKeys * hd * sizeof(__nv_bfloat16) + (size_t)nq * kMmaQ * kRawLd * sizeof(float) +
-         (size_t)nq * nq * sizeof(float);
+  const int cl = talking_mma_cluster(nq);
+  return (size_t)2 * (nkv / cl) * kMmaKeys * hd * sizeof(__nv_bfloat16) +
+         (size_t)(nq / cl) * kMmaQ * kRawLd * sizeof(float) + (size_t)(nq / cl) * nq * sizeof(float);
 }
 
-template <int HD>
+template <int HD, int CL>
 int launch_talking_mma(const void* q, const void* k_cache, const void* v_cache, void* out, const float* mix,
                        const int* cu_q, const int* pos0, const int* block_table, int bt_stride, int entry0,
                        int n_entries, int max_new, int nq, int nkv, int page_size, int num_pages, int window,
                        AttnExtra ex, int* status, cudaStream_t stream) {
   const size_t smem = talking_mma_smem(nq, nkv, HD);
-  cudaError_t e = cudaFuncSetAttribute(attention_talking_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(attention_talking_mma_kernel<HD, CL>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid((max_new + kMmaQ - 1) / kMmaQ, n_entries);
-  ccb_launch(attention_talking_mma_kernel<HD>, grid, dim3(nq * 32), smem, stream, (const __nv_bfloat16*)q,
-             (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, mix, cu_q, pos0,
-             block_table, bt_stride, entry0, nq, nkv, page_size, num_pages, window, ex, status);
+  dim3 grid(CL * ((max_new + kMmaQ - 1) / kMmaQ), n_entries);
+  if (CL == 1) {
+    ccb_launch(attention_talking_mma_kernel<HD, CL>, grid, dim3(nq * 32), smem, stream, (const __nv_bfloat16*)q,
+               (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, mix, cu_q, pos0,
+               block_table, bt_stride, entry0, nq, nkv, page_size, num_pages, window, ex, status);
+    return ccb_launch_status();
+  }
+  // a cluster of CL neighbouring blocks along x
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(nq / CL * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, attention_talking_mma_kernel<HD, CL>, (const __nv_bfloat16*)q,
+                     (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, mix, cu_q, pos0,
+                     block_table, bt_stride, entry0, nq, nkv, page_size, num_pages, window, ex, status);
   return ccb_launch_status();
 }
 
@@ -608,11 +651,14 @@ CCB_API int ccb_attention_talking(const void* q, const void* k_cache, const void
   return CCB_REFUSE_DTYPE;
 }
 
-// The tensor-core form for portions of prompts: bfloat16, head size 64 or 128, at most 16 heads (a warp each), and
-// shared memory for a tile of keys and of values of every kv head.
+// The tensor-core form for portions of prompts: bfloat16, head size 64 or 128, at most 16 heads a block (a warp
+// each) and at most two blocks a cluster (then heads and kv heads split in two), and shared memory for a tile of
+// keys and of values of the block's kv heads.
 CCB_API int ccb_attention_talking_mma_fits(int nq, int nkv, int hd) {
-  return nq > 0 && nq <= 16 && nkv > 0 && nq % nkv == 0 && (hd == 64 || hd == 128) &&
-         talking_mma_smem(nq, nkv, hd) <= 220 * 1024;
+  if (!(nq > 0 && nq <= 32 && nkv > 0 && nq % nkv == 0 && (hd == 64 || hd == 128))) return 0;
+  const int cl = talking_mma_cluster(nq);
+  if (nq % cl || nkv % cl) return 0;
+  return talking_mma_smem(nq, nkv, hd) <= 220 * 1024;
 }
 
 // Requests entry0 .. entry0 + n_entries - 1 of the step (none with more than max_new tokens); bfloat16.
@@ -626,9 +672,11 @@ CCB_API int ccb_attention_talking_mma(const void* q, const void* k_cache, const 
     return CCB_REFUSE_SIZE;
   if (mix == nullptr || (gate != nullptr && gate_stride < nq)) return CCB_REFUSE_ARG;
   AttnExtra ex{0, sink, gate, gate_stride};
-  if (hd == 128)
-    return launch_talking_mma<128>(q, k_cache, v_cache, out, mix, cu_q, pos0, block_table, bt_stride, entry0,
-                                   n_entries, max_new, nq, nkv, page_size, num_pages, window, ex, status, stream);
-  return launch_talking_mma<64>(q, k_cache, v_cache, out, mix, cu_q, pos0, block_table, bt_stride, entry0, n_entries,
-                                max_new, nq, nkv, page_size, num_pages, window, ex, status, stream);
+#define CCB_TALK_MMA(HD_, CL_)                                                                                       \
+  launch_talking_mma<HD_, CL_>(q, k_cache, v_cache, out, mix, cu_q, pos0, block_table, bt_stride, entry0, n_entries, \
+                               max_new, nq, nkv, page_size, num_pages, window, ex, status, stream)
+  const int cl = talking_mma_cluster(nq);
+  if (hd == 128) return cl == 1 ? CCB_TALK_MMA(128, 1) : CCB_TALK_MMA(128, 2);
+  return cl == 1 ? CCB_TALK_MMA(64, 1) : CCB_TALK_MMA(64, 2);
+#undef CCB_TALK_MMA
 }

@@ -259,10 +259,12 @@ def test_talking_attention_kernel(dtype, shape):
 
 
 @gpu
-@pytest.mark.parametrize("shape", [(16, 8, 128, 40), (4, 2, 64, 0), (6, 2, 64, 9), (12, 4, 128, 33), (1, 1, 64, 1)])
+@pytest.mark.parametrize("shape", [(16, 8, 128, 40), (4, 2, 64, 0), (6, 2, 64, 9), (12, 4, 128, 33), (1, 1, 64, 1),
+                                   (32, 8, 128, 40), (24, 4, 64, 0), (20, 2, 64, 7), (32, 32, 64, 33)])
 def test_talking_attention_on_tensor_cores(shape):
     """The tensor-core form for portions of prompts: two requests in one launch, one whole (70 tokens), one a
-    portion of 45 tokens after 25 cached ones, pages in a shuffled order, sink and gate."""
+    portion of 45 tokens after 25 cached ones, pages in a shuffled order, sink and gate.  More than 16 heads: two
+    blocks of a cluster, each with half of the heads, reading each other's raw scores."""
     from ccinfer_b200 import kernels
     nq, nkv, hd, window = shape
     assert kernels.attention_talking_mma_fits(torch.bfloat16, nq, nkv, hd)
