@@ -337,11 +337,18 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   __nv_bfloat16* v_s = k_s + (size_t)kv_local * kMmaKeys * HD;                   // the same for the values
   float* raw = reinterpret_cast<float*>(v_s + (size_t)kv_local * kMmaKeys * HD);  // [hpc][16][kRawLd]
   float* ms = raw + (size_t)hpc * kMmaQ * kRawLd;                                 // [hpc][nq]: the rows of its heads
-  const float* raw_of[CL];   // the raw scores of every block of the cluster (its own among them)
+  // In a cluster of two: a copy of the partner's raw scores of the tile.  They are fetched once a tile, 16 bytes a
+  // thread and access, rather than read in place by every warp (distributed shared memory is far slower than a
+  // block's own: with the partner's scores read in place the kernel took 3.4 times as long at 32 heads of 128).
+  float* partner_copy = ms + (size_t)hpc * nq;                                    // [hpc][16][kRawLd], CL == 2 only
+  const float* raw_of[CL];   // where this block reads the raw scores of each block's heads
+  const float* partner_raw = nullptr;
   raw_of[0] = raw;
   if constexpr (CL > 1) {
-#pragma unroll
-    for (int r = 0; r < CL; ++r) raw_of[r] = cg::this_cluster().map_shared_rank(raw, r);
+    static_assert(CL == 2, "a cluster of two");
+    partner_raw = cg::this_cluster().map_shared_rank(raw, rank ^ 1);
+    raw_of[rank] = raw;
+    raw_of[rank ^ 1] = partner_copy;
   }
 
   const int b = entry0 + blockIdx.y;
@@ -458,6 +465,12 @@ attention_talking_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     if constexpr (CL > 1) cg::this_cluster().sync(); else __syncthreads();
     if (it + 1 < n_tiles) issue(k_cache, k_s, first_tile + it + 1);
     cp_async_commit();
+    if constexpr (CL > 1) {
+      const float4* src = reinterpret_cast<const float4*>(partner_raw);
+      float4* dst = reinterpret_cast<float4*>(partner_copy);
+      for (int i = tid; i < hpc * kMmaQ * kRawLd / 4; i += n_threads) dst[i] = src[i];
+      __syncthreads();
+    }
     // this head's scores: the mix of all heads' raw ones (float), in the accumulator's layout
 #pragma unroll
     for (int nb = 0; nb < 4; ++nb) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
@@ -585,7 +598,7 @@ int talking_mma_cluster(int nq) { return nq <= 16 ? 1 : 2; }
 size_t talking_mma_smem(int nq, int nkv, int hd) {
   const int cl = talking_mma_cluster(nq);
   return (size_t)2 * (nkv / cl) * kMmaKeys * hd * sizeof(__nv_bfloat16) +
-         (size_t)(nq / cl) * kMmaQ * kRawLd * sizeof(float) + (size_t)(nq / cl) * nq * sizeof(float);
+         (size_t)cl * (nq / cl) * kMmaQ * kRawLd * sizeof(float) + (size_t)(nq / cl) * nq * sizeof(float);
 }
 
 template <int HD, int CL>
