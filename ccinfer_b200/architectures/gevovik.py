@@ -1,8 +1,8 @@
-"""Gevovik put together from the parts: state space layers, pairs of attention and delta rule side by side, and
+"""Gevovik put together from the parts: state space layers, pairs of an attention and a delta rule on the same input, and
 latent attention layers that may read an earlier layer's cached rows.
 
 A layer is a ``PostNormBlock``: h += norm1(mixer(h)); h += norm2(ff(h)), the sublayers reading the stream itself and
-each norm an RMS norm with ONE number as its weight.  The mixers: ``SelectiveStateSpace``; ``ParallelMixers`` of a
+each norm an RMS norm whose weight is a single scalar.  The mixers: ``SelectiveStateSpace``; ``ParallelMixers`` of a
 ``GroupedQueryAttention`` over a window (head norms, a rotation whose slow pairs are stretched, scores times a number
 per head and mixed over the heads before the softmax, a gate per head) and a ``ChannelGatedDelta``;
 ``LatentAttention`` over every earlier token with a sink, rotated in interleaved pairs, optionally without rows of

@@ -7,7 +7,7 @@
 Mixer types and their keys:
 
 * ``mamba2``: heads, vdim (channels per head), state, groups, conv (taps), norm_groups.
-* ``parallel``: left_scale, right_scale and two mixers side by side,
+* ``parallel``: left_scale, right_scale and a pair of mixers that run on the same input,
   ``left`` {heads, kv_heads, dim, vdim, scale, ``rot`` {dims, base, ``scaling`` {factor, original, fast, slow}},
   ``mask`` {size}}: softmax attention over a window whose heads' scores are mixed before the softmax, and
   ``right`` {heads, kv_heads, dim, vdim, conv}: the gated delta rule with a decay per key channel.  The ranks of

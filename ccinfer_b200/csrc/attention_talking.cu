@@ -37,7 +37,8 @@ using namespace ccb;
 
 namespace {
 
-constexpr int kTalkWarps = 8;
+constexpr int kTalkWarps = 16;   // (with 8 a warp had twice the heads, one after the other: 51 against 39 us a token,
+                                 // merge included, at 32 heads of 128 over a window of 1,024)
 constexpr int kTalkKeys = 32;
 
 template <typename T> struct Row8;   // eight neighbouring elements of a row as floats

@@ -494,7 +494,7 @@ CCB_API int ccb_relu_squared(void* act, const void* x, long long total, int dtyp
 }
 
 // ---------------------------------------------------------------------------------------------
-// out = sa * a + sb * b, elementwise in float (two mixers side by side, each with a constant factor).
+// out = sa * a + sb * b, elementwise in float (a pair of mixers on the same rows, each with a constant factor).
 template <typename T>
 __global__ void scaled_sum_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, float sa,
                                   float sb, size_t total) {

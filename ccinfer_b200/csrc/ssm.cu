@@ -2,14 +2,16 @@
 //
 // The input projection's rows are laid out [z | x | B | C | dt]: a gate z and an input x of `inner` = H P channels,
 // G groups of N channels each for B and C, and one step-size logit per head.  x, B and C pass a short causal
-// convolution per channel (with bias) and silu; dt = softplus(dt + dt_bias); a = exp(-exp(A_log_h) dt).  Head h
+// convolution per channel (with bias) followed by silu; the step size is softplus(logit + dt_bias[h]) and the decay
+// a = exp(-exp(A_log[h]) * step size).  Head h
 // (with group g = h / (H / G)) then runs
-//     S <- a_t S + B_t (dt_t x_t)^T        S [N, P], float, carried from token to token per request
+//     S <- a_t S + B_t (dt_t x_t)^T        S [N, P], float, kept per request between steps
 //     y_t = S^T C_t + D_h x_t
-// (the recurrence itself is ccb_ssm_recurrence in delta_rule.cu).  y is multiplied by silu(z), RMS-normed in
-// `parts` equal slices of the inner channels, each by its own root mean square, times a weight per channel.
+// (the recurrence itself is ccb_ssm_recurrence in delta_rule.cu).  Then y * silu(z) is cut into `parts` equal
+// slices of the inner channels, every slice divided by the root of its own mean square (+ eps), and a weight per
+// channel is applied.
 //
-//   ssm_prepare        a thread per (token, channel): convolution (earlier rows from the step or from the request's
+//   ssm_prepare        a thread per (token, channel), or per four channels where sizes and addresses allow: convolution (earlier rows from the step or from the request's
 //                      convolution state, which holds its last taps - 1 projected rows), bias, silu; float rows of x,
 //                      B, C, and per (token, head) dt and a
 //   conv_state_shift   a thread per (request, channel): the last taps - 1 projected rows of each request's portion
@@ -72,6 +74,77 @@ __global__ void ssm_prepare_kernel(const T* __restrict__ proj, int ld, int ox, i
     if (c < inner) xs[(size_t)t * inner + c] = v;
     else if (c < inner + gn) bs[(size_t)t * gn + (c - inner)] = v;
     else cs[(size_t)t * gn + (c - inner - gn)] = v;
+  }
+}
+
+
+// The same with four neighbouring channels a thread (every width, offset and row stride a multiple of 4, 16-byte
+// rows): 8- or 16-byte loads of the rows, 16-byte loads of the weights and stores of the results.
+template <typename T> struct In4;
+template <> struct In4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+};
+template <> struct In4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 a = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+  }
+};
+
+template <typename T>
+__global__ void ssm_prepare_vec_kernel(const T* __restrict__ proj, int ld, int ox, int odt,
+                                       const float* __restrict__ conv_w, const float* __restrict__ conv_b, int taps,
+                                       const T* __restrict__ conv_state, const float* __restrict__ A_log,
+                                       const float* __restrict__ dt_bias, const int* __restrict__ entry_of_token,
+                                       const int* __restrict__ cu_q, const int* __restrict__ state_slot,
+                                       float* __restrict__ xs, float* __restrict__ bs, float* __restrict__ cs,
+                                       float* __restrict__ dts, float* __restrict__ as, int rows, int H, int P, int G,
+                                       int N) {
+  ccb::pdl_begin();
+  const int inner = H * P, gn = G * N;
+  const int C = inner + 2 * gn;
+  const int C4 = C >> 2;
+  const int per_row = C4 + H;   // units of a token: groups of four channels, then one per head
+  const size_t total = (size_t)rows * per_row;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(i / per_row), u4 = (int)(i - (size_t)t * per_row);
+    const int e = entry_of_token[t];
+    if (u4 >= C4) {
+      const int h = u4 - C4;
+      float dt = 0.f, a = 1.f;
+      if (e >= 0) {
+        dt = softplus_acc(to_f32(proj[(size_t)t * ld + odt + h]) + dt_bias[h]);
+        a = expf(-expf(A_log[h]) * dt);
+      }
+      dts[(size_t)t * H + h] = dt;
+      as[(size_t)t * H + h] = a;
+      continue;
+    }
+    const int c = 4 * u4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (e >= 0) {
+      const int r0 = cu_q[e];
+      const int slot = state_slot[e];
+      float4 acc = conv_b ? *reinterpret_cast<const float4*>(conv_b + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int j = 0; j < taps; ++j) {
+        const int src = t - (taps - 1) + j;
+        float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (src >= r0) u = In4<T>::load(proj + (size_t)src * ld + ox + c);
+        else if (slot >= 0) u = In4<T>::load(conv_state + ((size_t)slot * (taps - 1) + (src - r0 + taps - 1)) * C + c);
+        const float4 wj = *reinterpret_cast<const float4*>(conv_w + (size_t)j * C + c);
+        acc.x = fmaf(wj.x, u.x, acc.x);
+        acc.y = fmaf(wj.y, u.y, acc.y);
+        acc.z = fmaf(wj.z, u.z, acc.z);
+        acc.w = fmaf(wj.w, u.w, acc.w);
+      }
+      v = make_float4(acc.x * sigmoid_acc(acc.x), acc.y * sigmoid_acc(acc.y), acc.z * sigmoid_acc(acc.z),
+                      acc.w * sigmoid_acc(acc.w));
+    }
+    float* dst = c < inner ? xs + (size_t)t * inner + c
+                           : (c < inner + gn ? bs + (size_t)t * gn + (c - inner) : cs + (size_t)t * gn + (c - inner - gn));
+    *reinterpret_cast<float4*>(dst) = v;
   }
 }
 
@@ -142,8 +215,28 @@ CCB_API int ccb_ssm_prepare(const void* proj, int ld, int ox, int odt, const flo
   if (rows <= 0) return 0;
   if (H <= 0 || P <= 0 || G <= 0 || N <= 0 || H % G || taps < 1 || taps > 64) return CCB_REFUSE_SIZE;
   if (proj == nullptr || conv_w == nullptr || (taps > 1 && conv_state == nullptr)) return CCB_REFUSE_ARG;
-  const size_t total = (size_t)rows * (H * P + 2 * G * N + H);
   const int threads = 256;
+  const int inner_ = H * P, gn_ = G * N;
+  const bool vec = inner_ % 4 == 0 && gn_ % 4 == 0 && ox % 4 == 0 && ld % 4 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(conv_state) |
+                     reinterpret_cast<uintptr_t>(conv_w) | reinterpret_cast<uintptr_t>(conv_b) |
+                     reinterpret_cast<uintptr_t>(xs) | reinterpret_cast<uintptr_t>(bs) |
+                     reinterpret_cast<uintptr_t>(cs)) & 15) == 0;
+  if (vec && (dtype == CCB_F32 || dtype == CCB_BF16)) {
+    const size_t total4 = (size_t)rows * ((inner_ + 2 * gn_) / 4 + H);
+    const size_t want4 = (total4 + threads - 1) / threads;
+    const int blocks4 = (int)(want4 < 148 * 32 ? want4 : 148 * 32);
+    if (dtype == CCB_F32)
+      ccb_launch(ssm_prepare_vec_kernel<float>, blocks4, threads, 0, stream, (const float*)proj, ld, ox, odt, conv_w,
+                 conv_b, taps, (const float*)conv_state, A_log, dt_bias, entry_of_token, cu_q, state_slot, xs, bs, cs,
+                 dts, as, rows, H, P, G, N);
+    else
+      ccb_launch(ssm_prepare_vec_kernel<__nv_bfloat16>, blocks4, threads, 0, stream, (const __nv_bfloat16*)proj, ld, ox,
+                 odt, conv_w, conv_b, taps, (const __nv_bfloat16*)conv_state, A_log, dt_bias, entry_of_token, cu_q,
+                 state_slot, xs, bs, cs, dts, as, rows, H, P, G, N);
+    return ccb_launch_status();
+  }
+  const size_t total = (size_t)rows * (H * P + 2 * G * N + H);
   const size_t want = (total + threads - 1) / threads;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
   if (dtype == CCB_F32)

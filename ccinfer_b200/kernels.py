@@ -816,8 +816,8 @@ def scaled_residual(h, delta, ls, y=None, w_next=None, eps_next: float = 0.0) ->
 # ---------------------------------------------------------------------------------------------
 def embed_pair(h, rows, table, pair_table, ids, positions, entry_of_token, cu_q, state_slot, prev_token, scale: float,
                buckets: int, mul_prev: int, mul_cur: int, n_entries: int, status=None, pending=None) -> None:
-    """h[t, :] = float(table[ids[t], :]) * scale + float(pair_table[row, :]) with row = (previous token * mul_prev +
-    token * mul_cur) mod buckets, or ``buckets`` at position 0; ``pair_table`` None: the first term alone.  The
+    """h[t, :] = float(table[ids[t], :]) * scale + float(pair_table[row, :]) with row = (mul_prev * previous +
+    mul_cur * ids[t]) % buckets, or ``buckets`` at position 0; ``pair_table`` None: the first term alone.  The
     previous token of a portion's first token is ``prev_token[slot]`` (int32 [slots]), which afterwards holds the
     portion's last token.  ``rows`` (optional): the same values in the storage type."""
     _cuda(h, rows, table, pair_table, ids, positions, entry_of_token, cu_q, state_slot, prev_token, status, pending)

@@ -233,7 +233,7 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     takes_unscaled = False   # True: ``forward`` hands x to ``Runtime.linear`` as it comes (it may be UnscaledRows)
-    out_key = "attn_out"     # the scratch buffer a mixer leaves its result in (two mixers side by side: one each)
+    out_key = "attn_out"     # the scratch buffer a mixer leaves its result in (a pair of mixers on the same rows: one each)
 
     def cache_need(self) -> Optional[CacheNeed]:
         return None

@@ -18,8 +18,8 @@ from .base import Part, Residual, StateNeed, TensorSpec
 class TokenEmbedding(Part):
     def __init__(self, vocab: int, hidden: int, weight_name: str, scale: float = 1.0, pair: dict = None):
         """``scale``: the rows are multiplied by it (in float).  ``pair`` {"name", "buckets", "mul_prev", "mul_cur"}:
-        a second table [buckets + 1, hidden] of which the row (previous token * mul_prev + token * mul_cur) mod
-        buckets is added, the last row for a sequence's first token.  The previous token is state of the request
+        a second table [buckets + 1, hidden]; the row added is hashed from the pair of tokens, (mul_prev * previous
+        + mul_cur * current) % buckets, and at position 0 it is the table's last row.  The previous token is state of the request
         (``state_need``): a portion's first token finds it there."""
         self.vocab, self.hidden, self.weight_name = int(vocab), int(hidden), weight_name
         self.scale = float(scale)

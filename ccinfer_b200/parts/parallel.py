@@ -1,4 +1,4 @@
-"""Two mixers side by side: both read the same rows, and their results are added with a constant factor each,
+"""A pair of mixers on the same rows, their results added with a constant factor each,
 
     out = left_scale * left(h) + right_scale * right(h).
 
@@ -15,7 +15,7 @@ from .base import Mixer
 class ParallelMixers(Mixer):
     def __init__(self, hidden: int, left: Mixer, right: Mixer, left_scale: float, right_scale: float):
         if left.cache_need() is not None and right.cache_need() is not None:
-            raise Unsupported("two mixers side by side: at most one of them keeps a paged cache")
+            raise Unsupported("a pair of mixers on the same rows: at most one of them keeps a paged cache")
         self.hidden, self.left, self.right = int(hidden), left, right
         self.left_scale, self.right_scale = float(left_scale), float(right_scale)
         # each half leaves its result in a buffer of its own

@@ -43,11 +43,14 @@ class RotaryHalf(PositionEncoding):
                  linear_scaling: float = None, query_temperature=None, ramp_scaling: dict = None):
         """``linear_scaling`` s: every frequency is divided by s (positions are stretched by s); the table is
         then evaluated in float64 and rounded once.  ``query_temperature``: see ``QueryTemperature``.
-        ``ramp_scaling`` {"factor", "original", "fast", "slow"}: only the slow pairs are stretched.  With
-        where(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(where(fast)), 0),
-        hi = min(ceil(where(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i
-        turns with f_i / factor * ramp_i + f_i (1 - ramp_i), and cosine and sine are both multiplied by
-        0.1 ln(factor) + 1 (``amplitude``; the attention mixer puts it into the weights of its head norms)."""
+        ``ramp_scaling`` {"factor", "original", "fast", "slow"}: only the slow pairs are stretched.  A pair that
+        makes ``w`` full turns over ``original`` positions has the (fractional) number
+        n(w) = rotary_dim * log(original / (w * 2 pi)) / (2 * log(theta)).  Pairs up to n(fast), rounded down and
+        not below 0, keep their frequency; pairs from n(slow) on, rounded up and not above rotary_dim - 1, have it
+        divided by ``factor``; between the two bounds the share b of the divided frequency grows linearly from 0 to
+        1 (the bounds are kept at least 0.001 apart), freq = b * f / factor + (1 - b) * f.  Cosine and sine both
+        carry the factor 1 + log(factor) / 10 (``amplitude``; the attention mixer puts it into the weights of its
+        head norms)."""
         rotary_dim = int(head_dim if rotary_dim is None else rotary_dim)
         self.ramp_scaling = None
         if ramp_scaling is not None:

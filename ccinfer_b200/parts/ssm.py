@@ -3,13 +3,13 @@
 With H heads of P channels (``inner`` = H P), a state of N channels per head and G groups of B and C:
 
     [z | x | B | C | dt] = Win h            z, x: inner;  B, C: G N;  dt: H
-    x | B | C  <-  silu(conv(x | B | C) + bias)     a causal convolution per channel over ``taps`` tokens, the last
-                                                    column of its weight the current token's, zeros before the start
+    x | B | C  <-  silu(conv(x | B | C) + bias)     per channel c: sum_j w[c, j] * u[t - (taps - 1) + j, c], inputs
+                                                    from before the sequence began counting as 0
     dt = softplus(dt + dt_bias);   a = exp(-exp(A_log_h) dt)
     S <- a_t S + B_t (dt_t x_t)^T;   y_t = S^T C_t + D_h x_t       per head h, with the B and C of group h // (H / G)
-    y <- (y * silu(z)) RMS-normed in ``norm_groups`` equal slices, times a weight per channel;   out = Wo y
+    y <- slices(y * silu(z)) each over the root of its mean square (+ eps), times a weight per channel;   out = Wo y
 
-The gate comes BEFORE the norm.  What a request keeps between steps: S [H, P, N] in float and the last
+There are ``norm_groups`` slices of equal size, and the gating by z is applied first, the norm second.  What a request keeps between steps: S [H, P, N] in float and the last
 ``taps - 1`` rows of x | B | C before the convolution.  Everything after the projection is float
 (``csrc/ssm.cu``; the recurrence is the plain form of ``csrc/delta_rule.cu`` with one decay per head and a step
 size on the write).

@@ -14,7 +14,7 @@ F64 = torch.float64
 
 
 def rms_unit(x, eps):
-    """x / sqrt(mean(x^2) + eps) over the last axis."""
+    """x over the root of (its mean square along the last axis, plus eps)."""
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
 
@@ -27,7 +27,7 @@ def softplus(x):
 
 
 def causal_conv(u, taps_w, bias=None):
-    """u [T, C], taps_w [C, taps] with the last column the current token's, zeros before the start."""
+    """u [T, C], taps_w [C, taps]: y[t] = sum_j taps_w[:, j] * u[t - (taps - 1) + j], with u = 0 at negative times."""
     T, C = u.shape
     taps = taps_w.shape[1]
     pad = torch.cat([torch.zeros((taps - 1, C), dtype=u.dtype), u], 0)

@@ -126,7 +126,7 @@ def test_plan_names_every_tensor_and_shares_the_latent_rows():
 
 def test_plain_rotation_frequencies():
     """Without scaling the frequencies are base^(-2i / dims); with it the fast pairs keep theirs, the slow ones are
-    divided by the factor, and both cosine and sine grow by 0.1 ln(factor) + 1."""
+    divided by the factor, and both cosine and sine carry 1 + ln(factor) / 10."""
     f, m = plain.rotary_frequencies({"dims": 8, "base": 100.0})
     assert m == 1.0 and np.allclose(f, [1.0, 100 ** -0.25, 0.1, 100 ** -0.75])
     f2, m2 = plain.rotary_frequencies({"dims": 8, "base": 100.0,
@@ -532,7 +532,7 @@ def test_a_far_token_decides_through_the_state(tmp_path):
 @gpu
 def test_the_pair_table_decides_across_portions(tmp_path):
     """The token's own row is nearly switched off, so the stream starts from the row that (previous token, token)
-    chooses: a wrong previous token at the start of a portion, or the wrong row for a sequence's first token,
+    chooses: a wrong previous token at the start of a portion, or the wrong row at position 0,
     changes every logit of that position."""
     cfg = _one_layer(plain.ssm(2, 8, 8, 1, 2, 1), ff=24, scale=0.01, bigram=(29, 7, 11))
     d = str(tmp_path / "pairs")
