@@ -323,6 +323,8 @@ ALONE = {
     "talking attention at tensor-core sizes": plain.pair(
         plain.talking(8, 4, 64, 64, 0.125, window=40, rot=(32, 10000.0), scaling=(2.0, 16, 4.0, 1.0)),
         plain.delta(2, 1, 16, 16, 4), 1.0, 0.3),
+    "twenty heads that talk: two blocks of a cluster": plain.pair(
+        plain.talking(20, 4, 64, 64, 0.125, window=33, rot=(64, 10000.0)), plain.delta(1, 1, 8, 8, 2), 1.0, 0.2),
     "latent attention": plain.latent(3, 8, 4, 8, 16, 0.3),
     "latent attention, tensor-core sizes": plain.latent(4, 16, 16, 32, 64, 0.2),
 }
