@@ -390,3 +390,52 @@ def random_weights(cfg, ranks, seed, sharp=1.0):
                 t = t * sharp
         w[name] = t.to(torch.bfloat16).to(torch.float32)
     return w
+
+
+def random_config(seed):
+    """A configuration drawn at random: (config, ranks, page size).  Every size, count, constant and option that a
+    configuration may state is drawn, the order of the layers too."""
+    import random
+    r = random.Random(seed)
+    width = r.choice([32, 40, 48, 64, 96])
+    layers, ranks, own_latents = [], {}, []
+    n_layers = r.randint(2, 6)
+    for i in range(n_layers):
+        kind = r.choice(["mamba2", "parallel", "latent_attention"])
+        if kind == "mamba2":
+            heads = r.choice([1, 2, 3, 4, 6, 8])
+            vdim = r.choice([4, 8, 16, 32])
+            groups = r.choice([g for g in (1, 2, 3, 4) if heads % g == 0])
+            norm_groups = r.choice([g for g in (1, 2, 3, heads) if (heads * vdim) % g == 0])
+            mix = ssm(heads, vdim, r.choice([4, 8, 16, 48, 64]), groups, r.randint(1, 4), norm_groups)
+        elif kind == "parallel":
+            kv = r.choice([1, 2, 4])
+            dim = r.choice([8, 16, 24, 32, 48, 64])
+            rot = scaling = None
+            if r.random() < 0.8:
+                rot = (r.choice([d for d in (2, 4, 8, 16, 32, 64, dim) if d <= dim]), r.choice([100.0, 10000.0, 500000.0]))
+                if r.random() < 0.6:
+                    scaling = (r.choice([1.5, 2.0, 8.0]), r.choice([8, 64, 512]), r.choice([4.0, 32.0]), r.choice([0.5, 1.0]))
+            window = r.choice([None, 1, 3, 7, 16, 33, 72])
+            left = talking(kv * r.choice([1, 2, 3]), kv, dim, r.choice([8, 16, 24, 32, 48, 64]),
+                           dim ** -0.5 * r.choice([0.7, 1.0, 1.6]), window=window, rot=rot, scaling=scaling)
+            kv2 = r.choice([1, 2])
+            right = delta(kv2 * r.choice([1, 2]), kv2, r.choice([4, 8, 16, 32]), r.choice([4, 8, 16, 32]), r.randint(1, 4))
+            mix = pair(left, right, r.choice([0.5, 0.8, 1.0]), r.choice([0.6, 0.9, 1.3]))
+            ranks[i] = (r.randint(2, 8), r.randint(2, 8))
+        else:
+            heads, dim, vdim = r.randint(1, 6), r.choice([4, 8, 16, 32, 64]), r.choice([4, 8, 16, 64])
+            if own_latents and r.random() < 0.5:
+                j = r.choice(own_latents)
+                src = layers[j][0][1]
+                mix = latent(heads, dim, src["rot_dim"], vdim, src["kv_rank"], r.choice([0.1, 0.2, 0.35]),
+                             base=src["rot"]["base"], kv_from=j)
+            else:
+                mix = latent(heads, dim, r.choice([2, 4, 8, 16]), vdim, r.choice([8, 16, 24, 32, 64]),
+                             r.choice([0.1, 0.2, 0.35]), base=r.choice([100.0, 10000.0, 1000000.0]))
+                own_latents.append(i)
+        layers.append((mix, r.choice([None, 16, 24, 40, 64, 100])))
+    bigram = (r.choice([7, 31, 53, 97]), r.randint(1, 40), r.randint(1, 40)) if r.random() < 0.7 else None
+    cfg = model(r.randint(50, 200), width, r.choice([1e-5, 1e-6]), layers,
+                scale=r.choice([1.0, 0.5, float(width) ** 0.5]), bigram=bigram)
+    return cfg, ranks, r.choice([4, 8, 16])
