@@ -1,8 +1,9 @@
 """Builds the CUDA extension in-tree with nvcc for sm_100a and returns the path of the shared object.
 
 Each ``.cu`` file is compiled to an object file on its own (in parallel) and the
-objects are linked into one ``libccinfer_b200_<group>.so`` under
-``ccinfer_b200/csrc/_build``.  A stamp made of the sources' contents and the
+objects of a group are linked into one ``libccinfer_b200_<group>.so`` under
+``ccinfer_b200/csrc/_build``; the kernels form several groups (families) that
+are built when first needed.  A stamp made of the sources' contents and the
 flags decides whether a build is current, so a library built on one machine is
 taken as it is on another with the same sources.  If the package folder cannot
 be written (a read-only install) the build goes to a per-user folder under the
@@ -26,27 +27,21 @@ from ..errors import ExtensionMissing
 
 CSRC = os.path.dirname(os.path.abspath(__file__))
 
-# group -> source files.  "core" is every kernel a model step needs; "host" is the C++ host core (cache manager,
-# request slots, the arrays of a step) behind the C interface of host/ccinfer.h: no device code in it.
+# group -> source files.  The kernels are built as FAMILIES, one shared object each, and a family is compiled and
+# loaded when one of its functions is first called (``kernels.lib()``): a model pays for the kernels it runs and no
+# others.  "base" is what every model needs (embedding, norms, rotation and cache write, the products, sampling,
+# random weights); "attention" the grouped-query attention kernels over keys and values; "recurrent" the short
+# convolutions and the recurrences with a state per request; "latent" attention over cached low-rank rows;
+# "talking" attention whose heads' scores are mixed before the softmax; "moe" the mixtures of experts.  "host" is
+# the C++ host core (cache manager, request slots, the arrays of a step) behind the C interface of host/ccinfer.h:
+# no device code in it.  Every kernel family also links pdl_flag.cu, its own copy of the launch switch.
+KERNEL_GROUPS = ("base", "attention", "recurrent", "latent", "talking", "moe")
+EVERY_KERNEL_GROUP = ["pdl_flag.cu"]
 GROUPS = {
-    "core": [
+    "base": [
         "elementwise.cu",
         "norm.cu",
         "rope_kv.cu",
-        "short_conv.cu",
-        "delta_rule.cu",
-        "linear_attention.cu",
-        "ssm.cu",
-        "latent_attention.cu",
-        "moe.cu",
-        "moe_tcgen05.cu",
-        "attention_generic.cu",
-        "attention_split.cu",
-        "attention_talking.cu",
-        "attention_decode_mma.cu",
-        "attention_decode_tma.cu",
-        "attention_prefill_mma.cu",
-        "attention_prefill_tc.cu",
         "gemm_f32.cu",
         "gemm_cublas.cu",
         "gemm_skinny.cu",
@@ -56,12 +51,31 @@ GROUPS = {
         "sampling.cu",
         "random_init.cu",
     ],
+    "attention": [
+        "attention_generic.cu",
+        "attention_split.cu",
+        "attention_decode_mma.cu",
+        "attention_decode_tma.cu",
+        "attention_prefill_mma.cu",
+        "attention_prefill_tc.cu",
+    ],
+    "recurrent": [
+        "short_conv.cu",
+        "delta_rule.cu",
+        "linear_attention.cu",
+        "ssm.cu",
+    ],
+    "latent": ["latent_attention.cu"],
+    "talking": ["attention_talking.cu"],
+    "moe": ["moe.cu", "moe_tcgen05.cu"],
     "host": [
         "host/host_core.cpp",
         "host/scheduler.cpp",
     ],
 }
-GROUP_LIBS = {"core": ["-lcublas"]}
+for _g in KERNEL_GROUPS:
+    GROUPS[_g] = GROUPS[_g] + EVERY_KERNEL_GROUP
+GROUP_LIBS = {"base": ["-lcublas"]}
 GROUP_HEADERS = {"host": ["host/ccinfer.h"]}   # default: every header beside the kernels
 
 NVCC_FLAGS = [
@@ -93,18 +107,27 @@ def _stamp(group: str) -> str:
     return h.hexdigest()
 
 
+_dir_lock = threading.Lock()
+_dir = None
+
+
 def _build_dir() -> str:
-    d = os.path.join(CSRC, "_build")
-    try:
-        os.makedirs(d, exist_ok=True)
-        probe = os.path.join(d, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.unlink(probe)
-        return d
-    except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"ccinfer_b200_build_{os.getuid()}")
-        os.makedirs(d, exist_ok=True)
+    """Where the shared objects go: decided once per process (several groups may be built side by side)."""
+    global _dir
+    with _dir_lock:
+        if _dir is not None:
+            return _dir
+        d = os.path.join(CSRC, "_build")
+        try:
+            os.makedirs(d, exist_ok=True)
+            probe = os.path.join(d, f".w{os.getpid()}")
+            with open(probe, "w"):
+                pass
+            os.unlink(probe)
+        except OSError:
+            d = os.path.join(tempfile.gettempdir(), f"ccinfer_b200_build_{os.getuid()}")
+            os.makedirs(d, exist_ok=True)
+        _dir = d
         return d
 
 
@@ -119,7 +142,7 @@ def _compile_one(nvcc: str, src: str, obj: str) -> None:
         raise ExtensionMissing(f"nvcc failed on {src}:\n{' '.join(cmd)}\n{r.stdout}")
 
 
-def library_path(group: str = "core", verbose: bool = True) -> str:
+def library_path(group: str = "base", verbose: bool = True) -> str:
     """Path of the up-to-date shared object of a group, building it if needed."""
     if group not in GROUPS:
         raise ExtensionMissing(f"unknown kernel group {group!r}")
@@ -174,10 +197,29 @@ def library_path(group: str = "core", verbose: bool = True) -> str:
     return lib
 
 
+def build_groups(groups, verbose: bool = True) -> list:
+    """Several groups at once (their files compile side by side); the paths in the order given."""
+    groups = list(groups)
+    if len(groups) <= 1:
+        return [library_path(g, verbose) for g in groups]
+    with concurrent.futures.ThreadPoolExecutor(max_workers=len(groups)) as ex:
+        return list(ex.map(lambda g: library_path(g, verbose), groups))
+
+
 def build_all(verbose: bool = True) -> list:
-    return [library_path(g, verbose) for g in GROUPS]
+    return build_groups(list(GROUPS), verbose)
 
 
 if __name__ == "__main__":
     for p in build_all():
         print(p)
+
+
+def exported_functions(group: str) -> list:
+    """Names of the functions a kernel group exports (``CCB_API <type> name(`` in its sources)."""
+    import re
+    names = []
+    for src in GROUPS[group]:
+        with open(os.path.join(CSRC, src)) as f:
+            names += re.findall(r"CCB_API\s+[A-Za-z_][A-Za-z0-9_ ]*?\b(ccb_[A-Za-z0-9_]+)\s*\(", f.read())
+    return names

@@ -171,7 +171,8 @@ __device__ __forceinline__ void set_status(int* status, int bit) {
 
 static inline int ccb_launch_status() { return (int)cudaGetLastError(); }
 
-// One switch for the whole library (ccb_set_pdl): launch kernels with programmatic stream serialization.
+// One switch per kernel family (ccb_set_pdl of its shared object; kernels.set_pdl tells every loaded family and every
+// family loaded later): launch kernels with programmatic stream serialization.
 extern int g_ccb_pdl;
 
 // `early`: this kernel gains from starting before its predecessor has finished (it prefetches weights).

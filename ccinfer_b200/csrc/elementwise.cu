@@ -8,14 +8,6 @@
 
 using namespace ccb;
 
-int g_ccb_pdl = 0;
-
-// 1: launch every kernel of the library so that it may overlap the end of its predecessor (see common.cuh)
-CCB_API int ccb_set_pdl(int on) {
-  g_ccb_pdl = on < 0 ? 0 : (on > 2 ? 2 : on);  // 1: products only; 2: every kernel
-  return 0;
-}
-
 template <typename T>
 __global__ void embed_gather_kernel(float* __restrict__ h, const T* __restrict__ table,
                                     const int* __restrict__ ids, int D, int V, const int* __restrict__ pending,

@@ -95,6 +95,8 @@ class Engine:
         self.vocab_size = plan.vocab_size
         self.rt = rt = Runtime(opt.device, self.dtype, opt.max_tokens_per_step, opt.max_requests)
         kernels.set_pdl(int(opt.use_pdl))
+        # the kernel families that the model's parts launch, built side by side if they are not there yet
+        kernels.prepare(g for part in plan.parts() for g in getattr(part, "kernel_groups", ()))
         for part in plan.parts():
             part.bind(rt, fetch)
 

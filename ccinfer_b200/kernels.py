@@ -178,8 +178,12 @@ _SIGNATURES = {
 }
 
 
-def lib(group: str = "core"):
-    """The loaded shared object of a kernel group (built at the first call)."""
+_pdl = None          # what set_pdl was last told: a family that is loaded later is told the same
+_group_of = {}       # exported function -> kernel family
+
+
+def _load(group: str):
+    """The loaded shared object of a kernel family (built at the first call)."""
     with _lock:
         if group in _libs:
             return _libs[group]
@@ -193,17 +197,62 @@ def lib(group: str = "core"):
             if fn is not None:
                 fn.argtypes = argtypes
                 fn.restype = c_int
+        handle.ccb_set_pdl.argtypes = [c_int]
+        handle.ccb_set_pdl.restype = c_int
+        if _pdl is not None:
+            handle.ccb_set_pdl(_pdl)
         _libs[group] = handle
         return handle
+
+
+class _Kernels:
+    """All kernel families as one object: ``lib().ccb_name`` finds the family that exports ``ccb_name`` (from the
+    sources' text), builds and loads it if this is its first use, and hands the function out.  A model therefore
+    compiles the families whose kernels it launches and no others."""
+
+    def __getattr__(self, name):
+        if not _group_of:
+            for group in _build.KERNEL_GROUPS:
+                for fn in _build.exported_functions(group):
+                    _group_of.setdefault(fn, group)
+        group = _group_of.get(name)
+        if group is None:
+            raise AttributeError(f"no kernel family exports {name!r}")
+        fn = getattr(_load(group), name)
+        setattr(self, name, fn)   # (found once)
+        return fn
+
+
+_kernels = _Kernels()
+
+
+def lib(group: str = None):
+    """The kernels (see ``_Kernels``), or with ``group`` the loaded shared object of that one family."""
+    if group is not None:
+        return _load(group)
+    _load("base")   # (what every model needs: a missing compiler shows here, before anything else happens)
+    return _kernels
+
+
+def prepare(groups) -> None:
+    """Builds (side by side) and loads the kernel families named, e.g. those a model's parts say they launch
+    (``Part.kernel_groups``), so that the first step does not build them one after another as it meets them."""
+    wanted = [g for g in dict.fromkeys(["base"] + list(groups)) if g not in _libs]
+    if len(wanted) > 1:
+        _build.build_groups(wanted)
+    for g in wanted:
+        _load(g)
 
 
 def set_pdl(on) -> None:
     """Launch the library's kernels so that each may start while its predecessor finishes (programmatic
     dependent launch); every kernel waits for its predecessor before it reads what that one wrote."""
-    fn = lib().ccb_set_pdl
-    fn.argtypes = [c_int]
-    fn.restype = c_int
-    fn(int(on))
+    global _pdl
+    _pdl = int(on)
+    with _lock:
+        loaded = list(_libs.values())
+    for handle in loaded:
+        handle.ccb_set_pdl(_pdl)
 
 
 def _stream() -> int:

@@ -57,6 +57,13 @@ from .base import CacheNeed, Mixer, PositionEncoding, StateNeed, TensorSpec
 class GroupedQueryAttention(Mixer):
     takes_unscaled = True
 
+    @property
+    def kernel_groups(self):
+        groups = ["talking"] if self.talking else ["attention"]
+        if self.taps or self.value_mix is not None:
+            groups.append("recurrent")   # (the short convolutions live there)
+        return tuple(groups)
+
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PositionEncoding, names: dict, qk_norm_eps: Optional[float] = None,
                  window: Optional[int] = None, own_kv: bool = True, scale: Optional[float] = None,

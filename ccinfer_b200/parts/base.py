@@ -123,6 +123,11 @@ class Part:
     #: step with this part is never replayed from a CUDA graph)
     graph_safe = True
 
+    #: kernel families beyond "base" that the part launches (``csrc/build.py: KERNEL_GROUPS``); the engine builds
+    #: the families of a model's parts side by side before the first step.  A part that names none still works:
+    #: a family is built when one of its kernels is first called.
+    kernel_groups = ()
+
 
 class Residual:
     """The residual stream of a step: ``h`` (float [T, D]) and a delta not yet added.

@@ -19,6 +19,10 @@ from .. import kernels
 from .base import Block, FeedForward, Mixer, Norm, Residual, ResidualSink
 
 
+def _groups_of(parts):
+    return tuple(dict.fromkeys(g for p in parts for g in getattr(p, "kernel_groups", ())))
+
+
 class PreNormBlock(Block):
     """h += Mixer(norm1(h)); h += FeedForward(norm2(h)); optionally, last, h += side(h, token).
 
@@ -39,6 +43,10 @@ class PreNormBlock(Block):
     @property
     def graph_safe(self):
         return all(p.graph_safe for p in self._parts())
+
+    @property
+    def kernel_groups(self):
+        return _groups_of(self._parts())
 
     def tensor_specs(self):
         return [s for p in self._parts() for s in p.tensor_specs()]
@@ -119,6 +127,10 @@ class SandwichNormBlock(Block):
     def graph_safe(self):
         return all(p.graph_safe for p in self._parts())
 
+    @property
+    def kernel_groups(self):
+        return _groups_of(self._parts())
+
     def tensor_specs(self):
         return [s for p in self._parts() for s in p.tensor_specs()]
 
@@ -183,6 +195,10 @@ class LayerScaleBlock(Block):
     @property
     def graph_safe(self):
         return all(p.graph_safe for p in self._parts())
+
+    @property
+    def kernel_groups(self):
+        return _groups_of(self._parts())
 
     def tensor_specs(self):
         from .base import TensorSpec
@@ -267,6 +283,10 @@ class PostNormBlock(Block):
     @property
     def graph_safe(self):
         return all(p.graph_safe for p in self._parts())
+
+    @property
+    def kernel_groups(self):
+        return _groups_of(self._parts())
 
     def tensor_specs(self):
         return [s for p in self._parts() for s in p.tensor_specs()]

@@ -36,6 +36,7 @@ def _pad8(n: int) -> int:
 
 
 class ChannelGatedDelta(Mixer):
+    kernel_groups = ("recurrent",)
     def __init__(self, hidden: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, taps: int,
                  norm_eps: float, names: dict):
         """``names``: tensor names under the keys q, k, v, o, q_conv, k_conv, v_conv, b, A_log, dt_bias, a1, a2,

@@ -36,6 +36,7 @@ def _pad8(n: int) -> int:
 
 
 class LatentAttention(Mixer):
+    kernel_groups = ("latent",)
     def __init__(self, hidden: int, heads: int, dim: int, rot_dim: int, value_dim: int, rank: int, window: int,
                  scale: float, rot_base: float, rot_dims: int, norm_eps: float, names: dict,
                  interleaved: bool = False, own_kv: bool = True):

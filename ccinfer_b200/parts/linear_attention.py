@@ -26,6 +26,7 @@ def _pad8(n: int) -> int:
 
 
 class GatedLinearAttention(Mixer):
+    kernel_groups = ("recurrent",)
     def __init__(self, hidden: int, heads: int, key_dim: int, value_dim: int, tau: float, decay_rank: int,
                  norm_eps: float, names: dict):
         """``names``: tensor names under the keys q, k, v, g, o, norm, a1, a2, a2_bias."""

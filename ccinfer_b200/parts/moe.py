@@ -35,6 +35,7 @@ from .base import FeedForward, TensorSpec
 
 
 class MixtureOfExperts(FeedForward):
+    kernel_groups = ("moe",)
     # From this many weights of the routed experts on, the sparse form runs.  Measured on B200, bfloat16, 32 experts
     # of which 4 are chosen, the whole part in us, dense / sparse at 1, 8, 256, 2,048 tokens: 16.8 M weights
     # 22 / 26, 24 / 31, 37 / 51, 138 / 99; 67 M weights 47 / 33, 48 / 42, 75 / 78, 340 / 187.

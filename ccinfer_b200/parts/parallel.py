@@ -27,6 +27,10 @@ class ParallelMixers(Mixer):
         return self.left.graph_safe and self.right.graph_safe
 
     @property
+    def kernel_groups(self):
+        return tuple(self.left.kernel_groups) + tuple(self.right.kernel_groups)
+
+    @property
     def own_kv(self):
         return getattr(self.left, "own_kv", False) or getattr(self.right, "own_kv", False)
 

@@ -24,6 +24,7 @@ from .base import Mixer, StateNeed, TensorSpec
 
 
 class SelectiveStateSpace(Mixer):
+    kernel_groups = ("recurrent",)
     def __init__(self, hidden: int, heads: int, head_dim: int, state: int, groups: int, taps: int, norm_groups: int,
                  norm_eps: float, names: dict):
         """``names``: tensor names under the keys in, conv, conv_bias, dt_bias, A_log, D, norm, o."""
