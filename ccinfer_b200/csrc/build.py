@@ -34,9 +34,10 @@ CSRC = os.path.dirname(os.path.abspath(__file__))
 # convolutions and the recurrences with a state per request; "latent" attention over cached low-rank rows;
 # "talking" attention whose heads' scores are mixed before the softmax; "moe" the mixtures of experts.  "host" is
 # the C++ host core (cache manager, request slots, the arrays of a step) behind the C interface of host/ccinfer.h:
-# no device code in it.  Every kernel family also links pdl_flag.cu, its own copy of the launch switch.
+# no device code in it.  Every kernel family also links pdl_flag.cu (its own copy of the launch switch) and
+# tma_host.cu (tensor maps for TMA, with a cache of its own).
 KERNEL_GROUPS = ("base", "attention", "recurrent", "latent", "talking", "moe")
-EVERY_KERNEL_GROUP = ["pdl_flag.cu"]
+EVERY_KERNEL_GROUP = ["pdl_flag.cu", "tma_host.cu"]
 GROUPS = {
     "base": [
         "elementwise.cu",
