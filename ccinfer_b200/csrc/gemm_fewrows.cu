@@ -245,6 +245,10 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
           for (int w = 0; w < FR_WARPS; ++w) sum += red[(w * 16 + f) * RED_LD + tok];
           if (scaled) sum *= s_scale[tok];
+          if (act.limit < 0.f) {   // a feed-forward without a gate: relu(.)^2 as the product's epilogue
+            sum = fmaxf(sum, 0.f);
+            sum *= sum;
+          }
           C[(size_t)tok * ldc + n0 + f] = from_f32<TOut>(sum);
         }
       }
@@ -353,6 +357,15 @@ CCB_API int ccb_gemm_fewrows_glu_bf16(void* C, const void* A, const void* W, int
   if (!(limit > 0.f)) return CCB_REFUSE_ARG;
   t_glu_act = CcbGluAct{limit, alpha, shift};
   const int rc = fewrows_checked(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, 1, CcbNormFuse{}, status, stream);
+  t_glu_act = CcbGluAct{0.f, 1.f, 0.f};
+  return rc;
+}
+
+// The plain product with relu(.)^2 as its epilogue (the activation of a feed-forward without a gate).
+CCB_API int ccb_gemm_fewrows_relu2_bf16(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw,
+                                        int ldc, int out_dtype, int* status, cudaStream_t stream) {
+  t_glu_act = CcbGluAct{-1.f, 0.f, 0.f};   // (limit < 0 names this epilogue in the kernel's plain branch)
+  const int rc = fewrows_checked(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, 0, CcbNormFuse{}, status, stream);
   t_glu_act = CcbGluAct{0.f, 1.f, 0.f};
   return rc;
 }

@@ -15,7 +15,9 @@
 //                      convolution state, which holds its last taps - 1 projected rows), bias, silu; float rows of x,
 //                      B, C, and per (token, head) dt and a
 //   conv_state_shift   a thread per (request, channel): the last taps - 1 projected rows of each request's portion
-//                      become its convolution state (run after ssm_prepare has read the old one)
+//                      become its convolution state (run after ssm_prepare has read the old one).  A request that
+//                      brings ONE token is moved on by ssm_prepare itself (`shift_single`): the thread of a channel is
+//                      the only one that reads that channel's state, so a decode step needs no second kernel
 //   ssm_gate_norm      a block per (token, slice): (o + D x) silu(z), its root mean square, the weight
 //
 // Everything after the projection is float; the projection's rows and the convolution state are of the storage type.
@@ -33,11 +35,12 @@ __device__ __forceinline__ float softplus_acc(float x) { return x > 20.f ? x : l
 template <typename T>
 __global__ void ssm_prepare_kernel(const T* __restrict__ proj, int ld, int ox, int odt,
                                    const float* __restrict__ conv_w, const float* __restrict__ conv_b, int taps,
-                                   const T* __restrict__ conv_state, const float* __restrict__ A_log,
+                                   const T* conv_state, const float* __restrict__ A_log,
                                    const float* __restrict__ dt_bias, const int* __restrict__ entry_of_token,
                                    const int* __restrict__ cu_q, const int* __restrict__ state_slot,
                                    float* __restrict__ xs, float* __restrict__ bs, float* __restrict__ cs,
-                                   float* __restrict__ dts, float* __restrict__ as, int rows, int H, int P, int G, int N) {
+                                   float* __restrict__ dts, float* __restrict__ as, int rows, int H, int P, int G, int N,
+                                   T* state_rw, int shift_single) {   // (state_rw is conv_state: no __restrict__ on either)
   ccb::pdl_begin();
   const int inner = H * P, gn = G * N;
   const int C = inner + 2 * gn;
@@ -70,6 +73,12 @@ __global__ void ssm_prepare_kernel(const T* __restrict__ proj, int ld, int ox, i
         acc = fmaf(conv_w[(size_t)j * C + c], u, acc);
       }
       v = acc * sigmoid_acc(acc);
+      // a request that brings one token: this thread is the only reader of its channel's state, which it moves on
+      if (shift_single && taps > 1 && slot >= 0 && cu_q[e + 1] - r0 == 1) {
+        T* st = state_rw + (size_t)slot * (taps - 1) * C + c;
+        for (int k = 0; k + 1 < taps - 1; ++k) st[(size_t)k * C] = st[(size_t)(k + 1) * C];
+        st[(size_t)(taps - 2) * C] = proj[(size_t)t * ld + ox + c];
+      }
     }
     if (c < inner) xs[(size_t)t * inner + c] = v;
     else if (c < inner + gn) bs[(size_t)t * gn + (c - inner)] = v;
@@ -96,12 +105,12 @@ template <> struct In4<__nv_bfloat16> {
 template <typename T>
 __global__ void ssm_prepare_vec_kernel(const T* __restrict__ proj, int ld, int ox, int odt,
                                        const float* __restrict__ conv_w, const float* __restrict__ conv_b, int taps,
-                                       const T* __restrict__ conv_state, const float* __restrict__ A_log,
+                                       const T* conv_state, const float* __restrict__ A_log,
                                        const float* __restrict__ dt_bias, const int* __restrict__ entry_of_token,
                                        const int* __restrict__ cu_q, const int* __restrict__ state_slot,
                                        float* __restrict__ xs, float* __restrict__ bs, float* __restrict__ cs,
                                        float* __restrict__ dts, float* __restrict__ as, int rows, int H, int P, int G,
-                                       int N) {
+                                       int N, T* state_rw, int shift_single) {   // (state_rw is conv_state: no __restrict__ on either)
   ccb::pdl_begin();
   const int inner = H * P, gn = G * N;
   const int C = inner + 2 * gn;
@@ -141,6 +150,12 @@ __global__ void ssm_prepare_vec_kernel(const T* __restrict__ proj, int ld, int o
       }
       v = make_float4(acc.x * sigmoid_acc(acc.x), acc.y * sigmoid_acc(acc.y), acc.z * sigmoid_acc(acc.z),
                       acc.w * sigmoid_acc(acc.w));
+      if (shift_single && taps > 1 && slot >= 0 && cu_q[e + 1] - r0 == 1) {   // (as in the kernel above)
+        T* st = state_rw + (size_t)slot * (taps - 1) * C + c;
+        for (int k = 0; k + 1 < taps - 1; ++k)
+          for (int x = 0; x < 4; ++x) st[(size_t)k * C + x] = st[(size_t)(k + 1) * C + x];
+        for (int x = 0; x < 4; ++x) st[(size_t)(taps - 2) * C + x] = proj[(size_t)t * ld + ox + c + x];
+      }
     }
     float* dst = c < inner ? xs + (size_t)t * inner + c
                            : (c < inner + gn ? bs + (size_t)t * gn + (c - inner) : cs + (size_t)t * gn + (c - inner - gn));
@@ -154,12 +169,12 @@ __global__ void ssm_prepare_vec_kernel(const T* __restrict__ proj, int ld, int o
 template <typename T>
 __global__ void conv_state_shift_kernel(const T* __restrict__ rows, int ld, int taps, int C, T* __restrict__ state,
                                         const int* __restrict__ cu_q, const int* __restrict__ state_slot,
-                                        int n_entries, int n_slots) {
+                                        int entry0, int n_entries, int n_slots) {
   ccb::pdl_begin();
   const int keep = taps - 1;
   const size_t total = (size_t)n_entries * C;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const int e = (int)(i / C), c = (int)(i - (size_t)e * C);
+    const int e = entry0 + (int)(i / C), c = (int)(i % C);
     const int slot = state_slot[e];
     if (slot < 0 || slot >= n_slots) continue;
     const int r0 = cu_q[e], n = cu_q[e + 1] - r0;
@@ -210,8 +225,8 @@ ssm_gate_norm_kernel(T* __restrict__ y, const float* __restrict__ o, const float
 CCB_API int ccb_ssm_prepare(const void* proj, int ld, int ox, int odt, const float* conv_w, const float* conv_b,
                             int taps, const void* conv_state, const float* A_log, const float* dt_bias,
                             const int* entry_of_token, const int* cu_q, const int* state_slot, float* xs, float* bs,
-                            float* cs, float* dts, float* as, int rows, int H, int P, int G, int N, int dtype,
-                            cudaStream_t stream) {
+                            float* cs, float* dts, float* as, int rows, int H, int P, int G, int N, int shift_single,
+                            int dtype, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (H <= 0 || P <= 0 || G <= 0 || N <= 0 || H % G || taps < 1 || taps > 64) return CCB_REFUSE_SIZE;
   if (proj == nullptr || conv_w == nullptr || (taps > 1 && conv_state == nullptr)) return CCB_REFUSE_ARG;
@@ -229,11 +244,11 @@ CCB_API int ccb_ssm_prepare(const void* proj, int ld, int ox, int odt, const flo
     if (dtype == CCB_F32)
       ccb_launch(ssm_prepare_vec_kernel<float>, blocks4, threads, 0, stream, (const float*)proj, ld, ox, odt, conv_w,
                  conv_b, taps, (const float*)conv_state, A_log, dt_bias, entry_of_token, cu_q, state_slot, xs, bs, cs,
-                 dts, as, rows, H, P, G, N);
+                 dts, as, rows, H, P, G, N, (float*)conv_state, shift_single);
     else
       ccb_launch(ssm_prepare_vec_kernel<__nv_bfloat16>, blocks4, threads, 0, stream, (const __nv_bfloat16*)proj, ld, ox,
                  odt, conv_w, conv_b, taps, (const __nv_bfloat16*)conv_state, A_log, dt_bias, entry_of_token, cu_q,
-                 state_slot, xs, bs, cs, dts, as, rows, H, P, G, N);
+                 state_slot, xs, bs, cs, dts, as, rows, H, P, G, N, (__nv_bfloat16*)conv_state, shift_single);
     return ccb_launch_status();
   }
   const size_t total = (size_t)rows * (H * P + 2 * G * N + H);
@@ -242,18 +257,19 @@ CCB_API int ccb_ssm_prepare(const void* proj, int ld, int ox, int odt, const flo
   if (dtype == CCB_F32)
     ccb_launch(ssm_prepare_kernel<float>, blocks, threads, 0, stream, (const float*)proj, ld, ox, odt, conv_w, conv_b,
                taps, (const float*)conv_state, A_log, dt_bias, entry_of_token, cu_q, state_slot, xs, bs, cs, dts, as,
-               rows, H, P, G, N);
+               rows, H, P, G, N, (float*)conv_state, shift_single);
   else if (dtype == CCB_BF16)
     ccb_launch(ssm_prepare_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)proj, ld, ox, odt,
                conv_w, conv_b, taps, (const __nv_bfloat16*)conv_state, A_log, dt_bias, entry_of_token, cu_q,
-               state_slot, xs, bs, cs, dts, as, rows, H, P, G, N);
+               state_slot, xs, bs, cs, dts, as, rows, H, P, G, N, (__nv_bfloat16*)conv_state, shift_single);
   else
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();
 }
 
 CCB_API int ccb_conv_state_shift(const void* rows, int ld, int taps, int C, void* state, const int* cu_q,
-                                 const int* state_slot, int n_entries, int n_slots, int dtype, cudaStream_t stream) {
+                                 const int* state_slot, int entry0, int n_entries, int n_slots, int dtype,
+                                 cudaStream_t stream) {
   if (n_entries <= 0 || taps <= 1) return 0;
   if (C <= 0) return CCB_REFUSE_SIZE;
   const size_t total = (size_t)n_entries * C;
@@ -262,10 +278,10 @@ CCB_API int ccb_conv_state_shift(const void* rows, int ld, int taps, int C, void
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
   if (dtype == CCB_F32)
     ccb_launch(conv_state_shift_kernel<float>, blocks, threads, 0, stream, (const float*)rows, ld, taps, C,
-               (float*)state, cu_q, state_slot, n_entries, n_slots);
+               (float*)state, cu_q, state_slot, entry0, n_entries, n_slots);
   else if (dtype == CCB_BF16)
     ccb_launch(conv_state_shift_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)rows, ld, taps,
-               C, (__nv_bfloat16*)state, cu_q, state_slot, n_entries, n_slots);
+               C, (__nv_bfloat16*)state, cu_q, state_slot, entry0, n_entries, n_slots);
   else
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();

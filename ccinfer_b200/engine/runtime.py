@@ -139,6 +139,21 @@ class Runtime:
         self.cublas.gemm_bf16(out, x, w)
         return out
 
+    def linear_relu2(self, out: torch.Tensor, x, w: torch.Tensor) -> torch.Tensor:
+        """out[M, N] = relu(x[M, K] @ w[N, K]^T)^2: with few rows in bfloat16 the activation is the epilogue of the
+        few-rows product, else the product and the activation kernel."""
+        x = self.rows(x)
+        M, K = x.shape
+        N = w.shape[0]
+        if (self.dtype == torch.bfloat16 and M <= kernels.SKINNY_MAX_ROWS and kernels.few_rows_product_kernel(
+                M, N, K, self.sm_count, kernels.gemm_tc_fits(K, x, w), kernels.gemm_fewrows_fits(M, K, x, w),
+                kernels.gemm_skinny_fits(M, K, x, w)) == "fewrows"):
+            kernels.gemm_fewrows_relu2_bf16(out, x, w, status=self.status)
+            return out
+        self.linear(out, x, w)
+        kernels.relu_squared(out, out)
+        return out
+
     def linear_batched(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """out[b] = x[b] @ w[b]^T for 3-d views [batch, M, *] (the heads of a layer, each with a matrix of its
         own); rows and batches may be strided; out may be float for bfloat16 operands."""

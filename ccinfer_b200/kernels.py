@@ -161,8 +161,11 @@ _SIGNATURES = {
     "ccb_init_random": [c_void_p, c_longlong, c_int, ctypes.c_ulonglong, ctypes.c_ulonglong, c_float, c_int, c_void_p],
     "ccb_ssm_prepare": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                        c_int, c_int, c_void_p],
-    "ccb_conv_state_shift": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+                        c_int, c_int, c_int, c_void_p],
+    "ccb_conv_state_shift": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_void_p],
+    "ccb_gemm_fewrows_relu2_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                    c_void_p, c_void_p],
     "ccb_ssm_gate_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_int, c_float, c_int, c_void_p],
     "ccb_ssm_recurrence": [c_void_p] * 9 + [c_int] * 5 + [c_void_p],
@@ -900,12 +903,13 @@ def scaled_sum(out, a, b, sa: float, sb: float) -> None:
 
 
 def ssm_prepare(proj, ox: int, odt: int, conv_w, conv_b, taps: int, conv_state, A_log, dt_bias, entry_of_token, cu_q,
-                state_slot, xs, bs, cs, dts, decay, H: int, P: int, G: int, N: int) -> None:
+                state_slot, xs, bs, cs, dts, decay, H: int, P: int, G: int, N: int, shift_single: bool = False) -> None:
     """The inputs of a selective state space recurrence from the input projection's rows ``proj`` [T, >=]: the
     channels x | B | C (from column ``ox``) pass the convolution ``conv_w`` [taps, channels] (+ ``conv_b``) and silu,
     rows before the step's first one coming from ``conv_state`` [slots, taps - 1, channels]; dt = softplus(proj[:,
     odt + h] + dt_bias[h]), decay = exp(-exp(A_log[h]) dt).  Outputs float: xs [T, H, P], bs and cs [T, G, N], dts
-    and decay [T, H]."""
+    and decay [T, H].  ``shift_single``: a request that brings one token has its convolution state moved on here
+    (then ``conv_state_shift`` is for the others only)."""
     _cuda(conv_w, conv_b, conv_state, A_log, dt_bias, entry_of_token, cu_q, state_slot, xs, bs, cs, dts, decay)
     T = xs.shape[0]
     C = H * P + 2 * G * N
@@ -914,20 +918,24 @@ def ssm_prepare(proj, ox: int, odt: int, conv_w, conv_b, taps: int, conv_state, 
     assert xs.dtype == bs.dtype == cs.dtype == dts.dtype == decay.dtype == torch.float32
     _check(lib().ccb_ssm_prepare(_p(proj), proj.stride(0), int(ox), int(odt), _p(conv_w), _p(conv_b), int(taps),
                                  _p(conv_state), _p(A_log), _p(dt_bias), _p(entry_of_token), _p(cu_q), _p(state_slot),
-                                 _p(xs), _p(bs), _p(cs), _p(dts), _p(decay), T, H, P, G, N, _dt(proj), _stream()),
-           "ssm_prepare")
+                                 _p(xs), _p(bs), _p(cs), _p(dts), _p(decay), T, H, P, G, N, 1 if shift_single else 0,
+                                 _dt(proj), _stream()), "ssm_prepare")
 
 
-def conv_state_shift(rows, taps: int, state, cu_q, state_slot, n_entries: int) -> None:
+def conv_state_shift(rows, taps: int, state, cu_q, state_slot, n_entries: int, entry0: int = 0) -> None:
     """After a convolution over a step's rows: the last taps - 1 of (the request's state rows, then its rows of this
-    step) become the state [slots, taps - 1, C]; ``rows`` [T, C] may be a column slice of wider rows."""
+    step) become the state [slots, taps - 1, C], for the entries entry0 .. entry0 + n_entries - 1; ``rows`` [T, C]
+    may be a column slice of wider rows."""
     _cuda(state, cu_q, state_slot)
     if taps <= 1:
         return
     C = rows.shape[1]
     assert rows.stride(1) == 1 and state.dtype == rows.dtype and tuple(state.shape[1:]) == (taps - 1, C)
+    if n_entries <= 0:
+        return
     _check(lib().ccb_conv_state_shift(_p(rows), rows.stride(0), int(taps), C, _p(state), _p(cu_q), _p(state_slot),
-                                      int(n_entries), state.shape[0], _dt(rows), _stream()), "conv_state_shift")
+                                      int(entry0), int(n_entries), state.shape[0], _dt(rows), _stream()),
+           "conv_state_shift")
 
 
 def ssm_recurrence(cs, bs, xs, decay, dts, state, out, cu_q, state_slot, n_entries: int, G: int, H: int, N: int,
@@ -1413,6 +1421,17 @@ def gemm_fewrows_bf16(c, a, w, swiglu: bool = False, status=None) -> None:
     assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
     _check(lib().ccb_gemm_fewrows_bf16(_p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), _dt(c),
                                        1 if swiglu else 0, _p(status), _stream()), "gemm_fewrows_bf16")
+
+
+def gemm_fewrows_relu2_bf16(c, a, w, status=None) -> None:
+    """c[M, N] = relu(a[M, K] @ w[N, K]^T)^2 for M <= 16: ``gemm_fewrows_bf16`` with the activation as its epilogue."""
+    _cuda(w, status)
+    assert a.dtype == w.dtype == torch.bfloat16 and c.dtype in _DT and c.is_cuda and a.is_cuda
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and c.shape == (M, N) and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    _check(lib().ccb_gemm_fewrows_relu2_bf16(_p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0),
+                                             _dt(c), _p(status), _stream()), "gemm_fewrows_relu2_bf16")
 
 
 def gemm_fewrows_blocks(N: int) -> int:

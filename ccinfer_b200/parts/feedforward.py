@@ -83,7 +83,6 @@ class SquaredReLU(FeedForward):
         x = rt.rows(x)
         T = x.shape[0]
         act = rt.scratch.get("ffn_act", (rt.max_tokens, self.inter), rt.dtype)[:T]
-        rt.linear(act, x, self.w_up)
-        kernels.relu_squared(act, act)
+        rt.linear_relu2(act, x, self.w_up)
         out = rt.scratch.get("ffn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
         return rt.linear(out, act, self.w_down)

@@ -91,9 +91,11 @@ class SelectiveStateSpace(Mixer):
         S, conv = state["S"], state["conv"]
         ox, odt = self.inner, self.inner + self.conv_width
         kernels.ssm_prepare(proj, ox, odt, self.conv_w, self.conv_b, self.taps, conv, self.A_log, self.dt_bias,
-                            step.entry_of_token, step.cu_q, step.state_slot, xs, bs, cs, dts, decay, H, P, G, N)
+                            step.entry_of_token, step.cu_q, step.state_slot, xs, bs, cs, dts, decay, H, P, G, N,
+                            shift_single=True)
+        # (requests that bring one token, which a step lists first, were moved on by the kernel above)
         kernels.conv_state_shift(proj[:, ox:ox + self.conv_width], self.taps, conv, step.cu_q, step.state_slot,
-                                 step.n_entries)
+                                 step.n_entries - step.n_single, entry0=step.n_single)
         o = rt.scratch.get("ssm_o", (rt.max_tokens, H, P), f32)[:T]
         kernels.ssm_recurrence(cs, bs, xs, decay, dts, S, o, step.cu_q, step.state_slot, step.n_entries, G, H, N, P)
         y = rt.scratch.get("ssm_y", (rt.max_tokens, self.inner), rt.dtype)[:T]

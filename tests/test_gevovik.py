@@ -177,6 +177,28 @@ def test_small_elementwise_kernels(dtype):
 
 
 @gpu
+@pytest.mark.parametrize("shape", [(1, 256, 2048), (7, 1000, 2048), (16, 512, 4096)])
+def test_squared_relu_as_the_epilogue_of_the_few_rows_product(shape):
+    """The product of a decode step's few rows with relu(.)^2 in its epilogue, and the runtime's choice of it."""
+    from ccinfer_b200 import kernels
+    from ccinfer_b200.engine.runtime import Runtime
+    M, N, K = shape
+    g = torch.Generator().manual_seed(N)
+    a = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16()
+    want = torch.relu(a.double() @ w.double().T) ** 2
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    kernels.gemm_fewrows_relu2_bf16(out, a.cuda(), w.cuda())
+    assert (out.cpu().double() - want).abs().max() < 2e-2 * max(1.0, float(want.abs().max()))
+    rt = Runtime("cuda:0", torch.bfloat16, 64, 16)
+    before = kernels.counters.own
+    out2 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    rt.linear_relu2(out2, a.cuda(), w.cuda())
+    assert (out2.cpu().double() - want).abs().max() < 2e-2 * max(1.0, float(want.abs().max()))
+    assert kernels.counters.own - before in (1, 2)   # (one kernel where the few-rows product runs)
+
+
+@gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_pair_embedding_kernel(dtype):
     """Two requests, one continuing after 5 tokens (its previous token comes from the state), one starting; then
